@@ -1,0 +1,121 @@
+/*
+ * texelator_b200 -- C ABI of the BC4 weight-linear operator for NVIDIA B200 (sm_100a).
+ *
+ * This is the drop-in boundary for the functions the reference binds with pybind11 in
+ * texelator/cuda/extension.cpp:7-48 (implemented there by texelator/cuda/texelator_cuda.cu).
+ * Plain pointers and sizes only: no torch types cross this interface.  Device pointers are raw
+ * CUDA device addresses, `stream` is a cudaStream_t passed as void*.
+ *
+ * Every function returns TX_OK (0) or a negative TX_E* code; tx_last_error() returns the message
+ * of the last failure on the calling thread (the reference raises TORCH_CHECK exceptions with the
+ * same meaning; the Python wrapper turns a non-zero status into RuntimeError).
+ *
+ * Threading: like the reference, a handle is not safe for concurrent use from several host
+ * threads, and setters are plain field writes.  All launches of one process on one device share
+ * a per-device split-K workspace, so tx_linear calls on the same device must be ordered on one
+ * stream (or otherwise serialised) with respect to each other.
+ */
+#ifndef TEXELATOR_B200_H
+#define TEXELATOR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TX_OK 0
+#define TX_EINVAL (-1)       /* bad argument (shape, dtype, null handle, ...) */
+#define TX_ECUDA (-2)        /* a CUDA runtime call failed */
+#define TX_EUNSUPPORTED (-3) /* feature not available on this device/build */
+#define TX_ESTATE (-4)       /* handle not in a state that allows the call */
+
+/* activation / bias element types (the reference accepts fp16 or bf16; this build computes the
+ * bf16 operator only -- fp16 activations return TX_EUNSUPPORTED) */
+#define TX_DTYPE_F16 0
+#define TX_DTYPE_BF16 1
+
+/* decode paths for tokens < prefill_threshold */
+#define TX_DECODE_ALU_MMA 0   /* in-register palette interpolation feeding mma.sync (default) */
+#define TX_DECODE_ALU_EXACT 1 /* per-weight bf16(pal*scale) with fp32 FMA, the reference's arithmetic */
+#define TX_DECODE_TEXTURE 2   /* signed-BC4 texture object + tex2Dgather, if the device offers it */
+
+/* tx_dequant output selectors */
+#define TX_DEQUANT_PALETTE_F32 0 /* unscaled palette value per weight, fp32 [M,K] */
+#define TX_DEQUANT_SCALED_F32 1  /* pal * scale_m, fp32 [M,K] */
+#define TX_DEQUANT_SCALED_BF16 2 /* bf16(pal * scale_m) [M,K] -- the matrix the operator multiplies by */
+
+const char *tx_last_error(void);
+
+/* Library / device facts: out[0]=ABI version, out[1]=compiled sm arch (100), out[2]=SM count of
+ * `device`, out[3]=1 if signed-BC4 texture views can be created on it, else 0. */
+int tx_runtime_info(int device, int64_t out[4]);
+
+/* pack_encoded(blocks, scales, bias) -> handle: texelator_cuda.cu:1260-1327 (extension.cpp:28-29).
+ * `blocks`: host, M * K/16 * 8 bytes, row-major BC4 blocks (encoder.py:105-117); `scales`: host,
+ * M floats; `bias_dev`: optional device pointer to M elements of `bias_dtype` (copied).  K is
+ * derived as 16 * nbytes / (8*M).  Copies are complete when the call returns. */
+int tx_pack_encoded(const uint8_t *blocks, size_t nbytes, const float *scales, int M,
+                    const void *bias_dev, int bias_dtype, int device, uint64_t *out_handle);
+
+/* Tensor-parallel variant (no counterpart in the reference, which is single-GPU): packs rows
+ * [row_begin,row_end) and 16-column blocks [kblock_begin,kblock_end) of a full M x K matrix.
+ * `scales` and `bias_dev` are indexed with the full-matrix row numbers. */
+int tx_pack_encoded_shard(const uint8_t *blocks, size_t nbytes, const float *scales, int M, int K,
+                          int row_begin, int row_end, int kblock_begin, int kblock_end,
+                          const void *bias_dev, int bias_dtype, int device, uint64_t *out_handle);
+
+/* linear(handle, x) -> y: texelator_cuda.cu:1329-1469 (extension.cpp:30).  `x` is a contiguous
+ * device [tokens, K] array, `y` a device [tokens, M] array the caller allocated (the reference
+ * allocates with at::empty); both of `dtype`.  Asynchronous on `stream`. */
+int tx_linear(uint64_t handle, const void *x, void *y, int tokens, int dtype, void *stream);
+
+/* set_lookahead: texelator_cuda.cu:1471-1478.  k in {1,2,3,4,6,8}: 1 KiB weight requests each
+ * warp keeps in flight (the reference: texture requests in flight). */
+int tx_set_lookahead(uint64_t handle, int lookahead);
+/* set_prefill: texelator_cuda.cu:1480-1488.  threshold >= 1; tile_rows >= 16 and % 16 == 0. */
+int tx_set_prefill(uint64_t handle, int threshold, int tile_rows);
+/* set_prefill_backend: texelator_cuda.cu:1490-1503.  0..4: streamed small-batch path in token
+ * groups; 5..9: tensor-core tile candidates #0..#4 (see tx_kernel_info). */
+int tx_set_prefill_backend(uint64_t handle, int backend);
+/* New: choose the decode path (TX_DECODE_*). TX_DECODE_TEXTURE fails with TX_EUNSUPPORTED when
+ * BC4 texture views are unavailable, and with TX_ESTATE when the hardware palette differs from
+ * the software palette (the reference's palette-hash gate, tuning.py:38-41). */
+int tx_set_decode_path(uint64_t handle, int path);
+
+/* handle_info: texelator_cuda.cu:1505-1512 -> [M, K, threshold, tile_rows, backend,
+ * pipelined_supported, graphics_supported]; the last two report [decode_path, lookahead] here
+ * (the reference's two flags describe kernels that do not exist in this build). */
+int tx_handle_info(uint64_t handle, int64_t out[7]);
+
+/* *_kernel_info(): texelator_cuda.cu:1514-1536, cutlass_texture_mainloop.cu:251-267 ->
+ * [numRegs, staticSmem, localBytes, maxThreads, dynamicSmem, tileM, tileN, tileK, activeBlocks/SM]
+ * for backend id 0 (decode GEMV) and 5..9 (prefill tile candidates). */
+int tx_kernel_info(int backend, int64_t out[9]);
+
+/* free: texelator_cuda.cu:1538.  The caller synchronises first (runtime.py:268-271). */
+int tx_free(uint64_t handle);
+
+/* palette_probe(): texelator_cuda.cu:1540-1595.  Measures the texture unit's BC4 palette:
+ * out_host[(e1+127)*255 + (e0+127)][selector], 65025*8 floats.  TX_EUNSUPPORTED when the device
+ * cannot create signed-BC4 texture views. */
+int tx_palette_probe(int device, float *out_host);
+/* Same table produced by this library's ALU decoder from the same probe blocks. */
+int tx_software_palette(int device, float *out_host);
+
+/* New: exact decode of the packed device copy (TX_DEQUANT_*), for bit-exact checks against the
+ * encoder's palette.  `out` is a device [M,K] array. */
+int tx_dequant(uint64_t handle, void *out, int what, void *stream);
+
+/* New: copies the BC4 blocks back out of the device layout into host row-major order
+ * (round-trip check of the packed copy). `out_host` holds M*K/2 bytes. */
+int tx_unpack_blocks(uint64_t handle, uint8_t *out_host);
+
+/* Number of this library's kernels launched by the calling process since load (all threads). */
+int64_t tx_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TEXELATOR_B200_H */

@@ -1,0 +1,134 @@
+// Shared declarations of the texelator_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "../../include/texelator_b200.h"
+
+namespace tx {
+
+// ---------------------------------------------------------------------------------------------
+// Device layout of the BC4 payload ("tiled"): the bytes of every 8-byte block are kept verbatim
+// (only an endpoint of -128 is stored as -127, which decodes identically under BC4-SNORM), but
+// blocks are re-ordered so that one warp-wide pair of 128-bit loads fetches a 16-row x 128-column
+// unit as 1 KiB of consecutive memory:
+//
+//   unit(rt, ki)  = 16 output rows [16rt, 16rt+16)  x  8 blocks [8ki, 8ki+8)      -> 1024 bytes
+//   byte offset   = (rt*KI + ki)*1024 + half*512 + lane*16 + sub*8
+//   lane = g*4+t  holds row 16rt + 8*half + g, blocks 8ki + t (sub 0) and 8ki + 4 + t (sub 1)
+//
+// This is the mma.sync m16n8k16 A-fragment ownership (lane (g,t) owns rows g and g+8), so decoded
+// weights go from registers to the tensor core with no shuffle.  Rows are padded to 16 and blocks
+// to 8 per row with a benign high-mode block (e0=1, e1=0, selectors 0); padded columns meet
+// zero activations and padded rows are never stored.
+// ---------------------------------------------------------------------------------------------
+constexpr int kUnitRows = 16;
+constexpr int kUnitBlocks = 8;
+constexpr int kUnitBytes = 1024;
+constexpr unsigned long long kPadBlock = 0x0000000000000001ull;  // e0=1, e1=0, selectors 0
+
+__host__ __device__ inline size_t tiled_block_offset(int row, int kb, int KI) {
+  int rt = row >> 4, half = (row >> 3) & 1, g = row & 7;
+  int ki = kb >> 3, sub = (kb >> 2) & 1, t = kb & 3;
+  return (size_t(rt) * KI + ki) * kUnitBytes + half * 512 + (g * 4 + t) * 16 + sub * 8;
+}
+
+struct Handle {
+  uint32_t magic = 0x54584234;  // "TXB4"
+  int M = 0, K = 0, blocks_per_row = 0, device = 0;
+  int MT = 0, KI = 0;           // row tiles of 16, k iterations of 128 columns
+  int lookahead = 2;            // texelator_cuda.cu:48 default
+  int prefill_threshold = 16, prefill_tile_rows = 1024, prefill_backend = 0;
+  int decode_path = TX_DECODE_ALU_MMA;
+  uint8_t *tiles = nullptr;     // MT*KI*1024 bytes
+  uint8_t *unit_flags = nullptr;  // MT*KI bytes: 1 if the unit holds a low-mode (e0<=e1) block
+  float *scales = nullptr;      // M
+  __nv_bfloat16 *bias = nullptr;  // M or null
+  int bias_dtype = TX_DTYPE_BF16;
+  // texture path (created on demand)
+  cudaArray_t array = nullptr;
+  cudaTextureObject_t texture = 0;
+};
+
+// Per-device scratch shared by every handle of the process on that device.
+struct Workspace {
+  float *partials = nullptr;      // split-K partial tiles
+  size_t partial_floats = 0;
+  unsigned *counters = nullptr;   // one arrival counter per row tile, all zero between launches
+  size_t counter_count = 0;
+  __half *xprep = nullptr;        // scaled fp16 activations of multi-token decode passes
+  size_t xprep_halfs = 0;
+  float *xmul = nullptr;          // per-token multipliers (64 floats)
+  int sm_count = 0;
+};
+
+void set_error(const std::string &message);
+int fail(int code, const std::string &message);
+Workspace *workspace_for(int device);  // allocates on first use (never inside a launch path)
+void count_launch(int n = 1);
+
+#define TX_CUDA(call)                                                                      \
+  do {                                                                                     \
+    cudaError_t tx_status_ = (call);                                                       \
+    if (tx_status_ != cudaSuccess)                                                         \
+      return ::tx::fail(TX_ECUDA, std::string(#call) + ": " + cudaGetErrorString(tx_status_)); \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// Exact software-palette decode of one selector (the table of oracle/bc4_oracle.py):
+// value = RN( ((7-g)*e0 + g*e1) / 889 ) in the high mode (e0 > e1),
+//         RN( ((5-g)*e0 + g*e1) / 635 ) in the low mode, selectors 6/7 -> -1/+1.
+// n*c followed by one fused residual correction is the correctly rounded quotient for every
+// numerator in [-889, 889] (checked exhaustively on the CPU), so no division is issued.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float rn_div_const(float n, float den, float rcp) {
+  float q = n * rcp;
+  float r = fmaf(-q, den, n);
+  return fmaf(r, rcp, q);
+}
+
+__device__ __forceinline__ float palette_value(int e0, int e1, int sel) {
+  e0 = max(e0, -127);
+  e1 = max(e1, -127);
+  if (e0 > e1) {
+    int g = sel == 0 ? 0 : (sel == 1 ? 7 : sel - 1);
+    int n = (7 - g) * e0 + g * e1;
+    return rn_div_const(float(n), 889.0f, 1.0f / 889.0f);
+  }
+  if (sel == 6) return -1.0f;
+  if (sel == 7) return 1.0f;
+  int g = sel == 0 ? 0 : (sel == 1 ? 5 : sel - 1);
+  int n = (5 - g) * e0 + g * e1;
+  return rn_div_const(float(n), 635.0f, 1.0f / 635.0f);
+}
+
+__device__ __forceinline__ int block_selector(unsigned long long block, int p) {
+  return int((block >> (16 + 3 * p)) & 7ull);
+}
+__device__ __forceinline__ int block_e0(unsigned long long block) { return int(int8_t(block & 0xff)); }
+__device__ __forceinline__ int block_e1(unsigned long long block) { return int(int8_t((block >> 8) & 0xff)); }
+
+// launchers implemented in the other translation units
+int launch_retile(const uint8_t *rowmajor_dev, Handle *h, cudaStream_t stream);
+int launch_untile(const Handle *h, uint8_t *rowmajor_dev, cudaStream_t stream);
+int launch_dequant(const Handle *h, void *out, int what, cudaStream_t stream);
+int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
+int launch_gemv_exact(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
+int launch_gemv_texture(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
+int launch_prefill_tile(const Handle *h, int backend, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens,
+                        cudaStream_t stream);
+bool prefill_tile_eligible(const Handle *h, int backend, int tokens);
+int gemv_kernel_info(int64_t out[9]);
+int prefill_kernel_info(int backend, int64_t out[9]);
+int texture_supported(int device);                       // 1 / 0
+int create_texture(Handle *h);                           // builds array + BC4 view from the tiled copy
+int probe_texture_palette(int device, float *out_host);  // TX_EUNSUPPORTED when views cannot be made
+int probe_software_palette(int device, float *out_host);
+
+}  // namespace tx

@@ -1,0 +1,648 @@
+// Decode GEMV for tokens < prefill_threshold (reference: texelator_bc4_bf16_kernel,
+// texelator/cuda/texelator_cuda.cu:141-199, one warp per output row through the texture unit).
+//
+// B200 design.  The kernel is a persistent stream-K sweep over 1 KiB units (16 rows x 128
+// columns) of the tiled BC4 payload.  Every warp owns a contiguous range of units, keeps LOOKAHEAD
+// units in flight as 128-bit loads, and turns each unit into eight mma.sync m16n8k16 A fragments
+// entirely in registers:
+//
+//   * per block, the two int8 endpoints become fp16x2 constants  base = 7*e0, delta = e1-e0
+//     (byte-permute into the fp16 "1024+u" encoding, then one HSUB2 / HFMA2; exact integers);
+//   * per pair of 3-bit selectors, one funnel shift + one LOP3 forms the address of a
+//     lane-replicated 64-entry shared-memory table that returns the remapped interpolation
+//     indices (g(s_lo), g(s_hi)) as fp16x2 -- bank = lane, so the lookup is conflict-free;
+//   * one HFMA2 gives the exact integer numerators n = base + g*delta (|n| <= 889, exact in fp16).
+//
+// Activations are converted once per CTA to fp16 after an exact power-of-two scaling per token
+// (so any bf16 range is safe), the tensor core accumulates n*x in fp32, and the epilogue applies
+// scale_m * 2^s / 889 and the bias before the single bf16 rounding.  The weights are therefore
+// never rounded to bf16: the result is the un-rounded BC4 linear, which differs from the
+// reference's bf16(pal*scale) arithmetic by that rounding only (rel-RMS about 1e-3).
+// Blocks in the low palette mode (e0 <= e1) are rare; units that contain one are flagged at pack
+// time and take a warp-uniform slow path with per-weight arithmetic.
+//
+// Row tiles whose K range is split over several warps are combined through a per-device scratch
+// buffer: every contributor stores its fp32 partial tile, and the last one to arrive (an atomic
+// counter per row tile) sums all partials in warp order, so results are deterministic.  There is
+// no spin-wait anywhere in this file.
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "tx_common.cuh"
+
+namespace tx {
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kLutBytes = 8192;
+constexpr int kMaxTokenTiles = 4;          // 8 tokens per tile
+constexpr int kXsPad = 16;                 // bytes added to the shared token stride (bank spread)
+constexpr size_t kSmemBudget = 200 * 1024; // dynamic shared memory we allow one CTA to take
+
+struct GemvParams {
+  const uint4 *tiles;
+  const uint8_t *flags;
+  const float *scales;
+  const __nv_bfloat16 *bias;
+  const __nv_bfloat16 *x;   // [T, K]
+  __nv_bfloat16 *y;         // [T, M]
+  const __half *xprep;      // [T, KP] pre-scaled fp16 activations (PRE) or null
+  const float *xmul;        // [T] 2^s/889 per token (PRE)
+  float *partials;
+  unsigned *counters;
+  int M, K, KI, T;
+  int KP;                   // KI * 128
+  long long units;          // MT * KI
+  int total_warps;
+};
+
+__device__ __forceinline__ unsigned lds32(unsigned addr) {
+  unsigned v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(unsigned addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                        unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned hfma2_u(unsigned a, unsigned b, unsigned c) {
+  unsigned d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned hsub2_u(unsigned a, unsigned b) {
+  unsigned d;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Eight fp16x2 numerator pairs of one block (positions 2i, 2i+1 in pair i), fast high-mode path.
+__device__ __forceinline__ void decode_block_fast(unsigned lo, unsigned hi, unsigned lut_lane, unsigned (&a)[8]) {
+  unsigned u = lo ^ 0x8080u;                               // endpoints as biased bytes e+128
+  unsigned e0m = __byte_perm(u, 0x64646464u, 0x4040);      // fp16x2 (1024+u0, 1024+u0)
+  unsigned e1m = __byte_perm(u, 0x64646464u, 0x4141);
+  unsigned delta = hsub2_u(e1m, e0m);                      // e1 - e0
+  unsigned base = hfma2_u(e0m, 0x47004700u, 0xEFE0EFE0u);  // 7*(1024+u0) - 8064 = 7*e0
+  unsigned f[8];
+  f[0] = lo >> 9;                                          // selector bits start at bit 16 of the block
+  f[1] = lo >> 15;
+  f[2] = __funnelshift_r(lo, hi, 21);
+  f[3] = hi << 5;
+  f[4] = hi >> 1;
+  f[5] = hi >> 7;
+  f[6] = hi >> 13;
+  f[7] = hi >> 19;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    unsigned g2 = lds32((f[i] & 0x1F80u) | lut_lane);
+    a[i] = hfma2_u(g2, delta, base);
+  }
+}
+
+// Generic path: any mode, per-weight fp32 arithmetic, value = 889 * palette rounded to fp16.
+__device__ __noinline__ void decode_block_slow(unsigned lo, unsigned hi, unsigned (&a)[8]) {
+  unsigned long long block = (unsigned long long)lo | ((unsigned long long)hi << 32);
+  int e0 = block_e0(block), e1 = block_e1(block);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float v[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      int s = block_selector(block, 2 * i + q);
+      if (e0 > e1) {
+        int g = s == 0 ? 0 : (s == 1 ? 7 : s - 1);
+        v[q] = float((7 - g) * e0 + g * e1);
+      } else if (s >= 6) {
+        v[q] = s == 6 ? -889.0f : 889.0f;
+      } else {
+        int g = s == 0 ? 0 : (s == 1 ? 5 : s - 1);
+        v[q] = float((5 - g) * e0 + g * e1) * 1.4f;       // 889/635
+      }
+    }
+    __half2 h = __floats2half2_rn(v[0], v[1]);
+    a[i] = *reinterpret_cast<unsigned *>(&h);
+  }
+}
+
+__device__ __forceinline__ bool block_is_low(unsigned lo) {
+  return int(int8_t(lo & 0xff)) <= int(int8_t((lo >> 8) & 0xff));
+}
+
+// amax of |x| over one token row, as the integer order of bf16 magnitudes
+__device__ __forceinline__ unsigned chunk_absmax(uint4 c) {
+  unsigned m = 0;
+  unsigned w[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m = max(m, w[i] & 0x7fffu);
+    m = max(m, (w[i] >> 16) & 0x7fffu);
+  }
+  return m;
+}
+
+// power-of-two scaling that brings a row with bf16 magnitude pattern `amax_bits` below 2^15
+__device__ __forceinline__ void token_scaling(unsigned amax_bits, float &mult, float &inverse) {
+  int ex = int(amax_bits >> 7) & 0xff;
+  if (amax_bits == 0) ex = 141;
+  ex = min(max(ex, 15), 254);
+  mult = __int_as_float((268 - ex) << 23);      // 2^(14 - (ex-127))
+  inverse = __int_as_float((ex - 14) << 23);    // 2^((ex-127) - 14)
+}
+
+__device__ __forceinline__ uint4 convert_chunk(uint4 c, float mult) {
+  unsigned w[4] = {c.x, c.y, c.z, c.w};
+  unsigned o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float lo = __uint_as_float(w[i] << 16) * mult;
+    float hi = __uint_as_float(w[i] & 0xffff0000u) * mult;
+    __half2 h = __floats2half2_rn(lo, hi);
+    o[i] = *reinterpret_cast<unsigned *>(&h);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Pre-pass for larger token counts: one CTA per token writes scaled fp16 activations and the
+// per-token multiplier 2^s/889 to scratch.
+__global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ xprep,
+                                                                 float *__restrict__ xmul, int K, int KP) {
+  __shared__ unsigned warp_max[kGemvWarps];
+  int tok = blockIdx.x;
+  const uint4 *src = reinterpret_cast<const uint4 *>(x + size_t(tok) * K);
+  int chunks = K / 8, padded = KP / 8;
+  unsigned m = 0;
+  for (int i = threadIdx.x; i < chunks; i += kGemvThreads) m = max(m, chunk_absmax(src[i]));
+  m = __reduce_max_sync(0xffffffffu, m);
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = 0;
+#pragma unroll
+  for (int w = 0; w < kGemvWarps; ++w) m = max(m, warp_max[w]);
+  float mult, inverse;
+  token_scaling(m, mult, inverse);
+  if (threadIdx.x == 0) xmul[tok] = inverse * (1.0f / 889.0f);
+  uint4 *dst = reinterpret_cast<uint4 *>(xprep + size_t(tok) * KP);
+  for (int i = threadIdx.x; i < padded; i += kGemvThreads)
+    dst[i] = i < chunks ? convert_chunk(src[i], mult) : make_uint4(0, 0, 0, 0);
+}
+
+template <int NT>
+__device__ __forceinline__ void store_tile(const GemvParams &p, const float (&acc)[NT][4], const float *tokmul, int rt, int lane) {
+  int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    int row = rt * 16 + half * 8 + g;
+    if (row >= p.M) continue;
+    float scale = p.scales[row];
+    float bias = p.bias ? __bfloat162float(p.bias[row]) : 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        int tok = nt * 8 + 2 * t + q;
+        if (tok < p.T) p.y[size_t(tok) * p.M + row] = __float2bfloat16(fmaf(acc[nt][half * 2 + q], scale * tokmul[tok], bias));
+      }
+  }
+}
+
+template <int LOOKAHEAD, int NT, bool PRE>
+__global__ void __launch_bounds__(kGemvThreads, PRE || NT > 1 ? 1 : 2) gemv_mma_kernel(const GemvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const unsigned sbase = unsigned(__cvta_generic_to_shared(smem_raw));
+  const unsigned lut_s = (sbase + kLutBytes - 1) & ~unsigned(kLutBytes - 1);
+  uint8_t *lut_g = smem_raw + (lut_s - sbase);
+  float *tokmul = reinterpret_cast<float *>(lut_g + kLutBytes);  // 32 floats
+  unsigned *red = reinterpret_cast<unsigned *>(lut_g + kLutBytes + 128);  // 8 words
+  uint8_t *xs_g = lut_g + kLutBytes + 256;
+  const unsigned xs_s = lut_s + kLutBytes + 256;
+  const unsigned xs_stride = unsigned(p.KP) * 2 + kXsPad;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  // -- this warp's contiguous unit range (stream-K) and the first loads, issued before anything else
+  const long long gw = (long long)blockIdx.x * kGemvWarps + warp;
+  const bool has_work = gw < p.total_warps;
+  const long long u0 = has_work ? p.units * gw / p.total_warps : 0;
+  const long long u1 = has_work ? p.units * (gw + 1) / p.total_warps : 0;
+  uint4 pend[LOOKAHEAD][2];
+  unsigned pflag[LOOKAHEAD];
+  const uint4 *src = p.tiles + u0 * 64 + lane;
+#pragma unroll
+  for (int i = 0; i < LOOKAHEAD; ++i) {
+    if (u0 + i < u1) {
+      pend[i][0] = ldg_stream(src + size_t(i) * 64);
+      pend[i][1] = ldg_stream(src + size_t(i) * 64 + 32);
+      pflag[i] = p.flags[u0 + i];
+    }
+  }
+
+  // -- selector-pair table: entry idx holds fp16x2 (g(idx & 7), g(idx >> 3)), replicated per lane
+  for (int i = tid; i < 64 * 32; i += kGemvThreads) {
+    int idx = i >> 5, s0 = idx & 7, s1 = idx >> 3;
+    float g0 = s0 == 0 ? 0.f : (s0 == 1 ? 7.f : float(s0 - 1));
+    float g1 = s1 == 0 ? 0.f : (s1 == 1 ? 7.f : float(s1 - 1));
+    reinterpret_cast<__half2 *>(lut_g)[i] = __floats2half2_rn(g0, g1);
+  }
+
+  // -- activations -> fp16 in shared memory
+  const int chunks = p.K / 8, padded = p.KP / 8;
+  if (PRE) {
+    for (int tok = 0; tok < p.T; ++tok) {
+      const uint4 *xp = reinterpret_cast<const uint4 *>(p.xprep + size_t(tok) * p.KP);
+      uint4 *dst = reinterpret_cast<uint4 *>(xs_g + size_t(tok) * xs_stride);
+      for (int i = tid; i < padded; i += kGemvThreads) dst[i] = xp[i];
+    }
+    if (tid < p.T) tokmul[tid] = p.xmul[tid];
+  } else {
+    for (int tok = 0; tok < p.T; ++tok) {
+      const uint4 *xp = reinterpret_cast<const uint4 *>(p.x + size_t(tok) * p.K);
+      unsigned m = 0;
+#pragma unroll 4
+      for (int i = tid; i < chunks; i += kGemvThreads) m = max(m, chunk_absmax(xp[i]));
+      m = __reduce_max_sync(0xffffffffu, m);
+      if (lane == 0) red[warp] = m;
+      __syncthreads();
+      m = 0;
+#pragma unroll
+      for (int w = 0; w < kGemvWarps; ++w) m = max(m, red[w]);
+      float mult, inverse;
+      token_scaling(m, mult, inverse);
+      if (tid == 0) tokmul[tok] = inverse * (1.0f / 889.0f);
+      uint4 *dst = reinterpret_cast<uint4 *>(xs_g + size_t(tok) * xs_stride);
+#pragma unroll 4
+      for (int i = tid; i < padded; i += kGemvThreads)
+        dst[i] = i < chunks ? convert_chunk(xp[i], mult) : make_uint4(0, 0, 0, 0);
+      __syncthreads();
+    }
+  }
+  __syncthreads();
+  if (u0 >= u1) return;
+
+  const unsigned lut_lane = lut_s + lane * 4;
+  // shared address of this lane's activations for token tile 0 (token g); inactive lanes feed zeros
+  unsigned xs_lane[NT];
+  bool tok_ok[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    tok_ok[nt] = nt * 8 + g < p.T;
+    xs_lane[nt] = xs_s + unsigned(nt * 8 + g) * xs_stride + t * 32;
+  }
+
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) acc[nt][q] = 0.f;
+
+  int rt = int(u0 / p.KI), ki = int(u0 % p.KI);
+  int seg_first = ki;
+  long long u = u0;
+  while (u < u1) {
+#pragma unroll
+    for (int slot = 0; slot < LOOKAHEAD; ++slot) {
+      if (u >= u1) break;
+      uint4 q = pend[slot][0], r = pend[slot][1];
+      unsigned flag = pflag[slot];
+      if (u + LOOKAHEAD < u1) {
+        const uint4 *next = p.tiles + (u + LOOKAHEAD) * 64 + lane;
+        pend[slot][0] = ldg_stream(next);
+        pend[slot][1] = ldg_stream(next + 32);
+        pflag[slot] = p.flags[u + LOOKAHEAD];
+      }
+      // ---- one unit: blocks (ki*8 + t) [sub 0] and (ki*8 + 4 + t) [sub 1] of rows g and g+8
+      const unsigned xoff = unsigned(ki) * 256;
+#pragma unroll
+      for (int sub = 0; sub < 2; ++sub) {
+        unsigned qlo = sub ? q.z : q.x, qhi = sub ? q.w : q.y;
+        unsigned rlo = sub ? r.z : r.x, rhi = sub ? r.w : r.y;
+        unsigned aq[8], ar[8];
+        if (flag) {
+          if (block_is_low(qlo)) decode_block_slow(qlo, qhi, aq); else decode_block_fast(qlo, qhi, lut_lane, aq);
+          if (block_is_low(rlo)) decode_block_slow(rlo, rhi, ar); else decode_block_fast(rlo, rhi, lut_lane, ar);
+        } else {
+          decode_block_fast(qlo, qhi, lut_lane, aq);
+          decode_block_fast(rlo, rhi, lut_lane, ar);
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          uint4 b0 = make_uint4(0, 0, 0, 0), b1 = make_uint4(0, 0, 0, 0);
+          if (tok_ok[nt]) {
+            b0 = lds128(xs_lane[nt] + xoff + sub * 128);
+            b1 = lds128(xs_lane[nt] + xoff + sub * 128 + 16);
+          }
+          mma_f16(acc[nt], aq[0], ar[0], aq[1], ar[1], b0.x, b0.y);
+          mma_f16(acc[nt], aq[2], ar[2], aq[3], ar[3], b0.z, b0.w);
+          mma_f16(acc[nt], aq[4], ar[4], aq[5], ar[5], b1.x, b1.y);
+          mma_f16(acc[nt], aq[6], ar[6], aq[7], ar[7], b1.z, b1.w);
+        }
+      }
+      // ---- end of a row tile segment?
+      if (ki == p.KI - 1 || u == u1 - 1) {
+        bool whole = seg_first == 0 && ki == p.KI - 1;
+        if (whole) {
+          store_tile<NT>(p, acc, tokmul, rt, lane);
+        } else {
+          // partial segment: slot 0 if this warp's range starts inside the tile, else slot 1
+          int which = u0 >= (long long)rt * p.KI ? 0 : 1;
+          float *mine = p.partials + (size_t(gw) * 2 + which) * (NT * 128);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd) mine[(nt * 4 + qd) * 32 + lane] = acc[nt][qd];
+          __threadfence();
+          __syncwarp();
+          long long first_unit = (long long)rt * p.KI, last_unit = first_unit + p.KI - 1;
+          long long wf = ((first_unit + 1) * p.total_warps - 1) / p.units;
+          long long wl = ((last_unit + 1) * p.total_warps - 1) / p.units;
+          unsigned arrived = 0;
+          if (lane == 0) arrived = atomicAdd(&p.counters[rt], 1u);
+          arrived = __shfl_sync(0xffffffffu, arrived, 0);
+          if (arrived == unsigned(wl - wf)) {
+            __threadfence();
+            float sum[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+              for (int qd = 0; qd < 4; ++qd) sum[nt][qd] = 0.f;
+            for (long long w = wf; w <= wl; ++w) {
+              long long ws = p.units * w / p.total_warps;
+              int wslot = ws >= first_unit ? 0 : 1;
+              const float *theirs = p.partials + (size_t(w) * 2 + wslot) * (NT * 128);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) sum[nt][qd] += __ldcg(theirs + (nt * 4 + qd) * 32 + lane);
+            }
+            store_tile<NT>(p, sum, tokmul, rt, lane);
+            if (lane == 0) p.counters[rt] = 0;   // ready for the next launch
+          }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int qd = 0; qd < 4; ++qd) acc[nt][qd] = 0.f;
+        seg_first = 0;   // every later segment of this warp starts at the first column unit
+      }
+      ++u;
+      if (++ki == p.KI) {
+        ki = 0;
+        ++rt;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Reference-arithmetic GEMV (TX_DECODE_ALU_EXACT): w = bf16(pal*scale), fp32 FMA, one warp per
+// row (texelator_cuda.cu:141-199 without the texture unit).  Correctness path, not tuned.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gemv_exact_kernel(const unsigned long long *__restrict__ tiles,
+                                                         const float *__restrict__ scales,
+                                                         const __nv_bfloat16 *__restrict__ bias,
+                                                         const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y,
+                                                         int M, int K, int bpr, int KI) {
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int row = blockIdx.x * 8 + warp, token = blockIdx.y;
+  if (row >= M) return;
+  x += size_t(token) * K;
+  float scale = scales[row];
+  float a0 = 0.f, a1 = 0.f;
+  for (int kb = lane; kb < bpr; kb += 32) {
+    unsigned long long block = tiles[tiled_block_offset(row, kb, KI) >> 3];
+    int e0 = block_e0(block), e1 = block_e1(block);
+#pragma unroll
+    for (int p = 0; p < 16; p += 2) {
+      float w0 = __bfloat162float(__float2bfloat16(__fmul_rn(palette_value(e0, e1, block_selector(block, p)), scale)));
+      float w1 = __bfloat162float(__float2bfloat16(__fmul_rn(palette_value(e0, e1, block_selector(block, p + 1)), scale)));
+      a0 = fmaf(w0, __bfloat162float(x[kb * 16 + p]), a0);
+      a1 = fmaf(w1, __bfloat162float(x[kb * 16 + p + 1]), a1);
+    }
+  }
+  float acc = a0 + a1;
+  for (int d = 16; d; d >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, d);
+  if (lane == 0) y[size_t(token) * M + row] = __float2bfloat16(acc + (bias ? __bfloat162float(bias[row]) : 0.f));
+}
+
+int launch_gemv_exact(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream) {
+  for (int t0 = 0; t0 < tokens; t0 += 65535) {
+    int n = std::min(tokens - t0, 65535);
+    dim3 grid((h->M + 7) / 8, n);
+    gemv_exact_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const unsigned long long *>(h->tiles), h->scales, h->bias,
+                                                x + size_t(t0) * h->K, y + size_t(t0) * h->M, h->M, h->K,
+                                                h->blocks_per_row, h->KI);
+    count_launch();
+  }
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Texture GEMV (TX_DECODE_TEXTURE): signed-BC4 texture object, tex2Dgather, one warp per row.
+// Own mapping: lane = block within a 32-block stride, four gathers per block.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gemv_texture_kernel(cudaTextureObject_t texture, const float *__restrict__ scales,
+                                                           const __nv_bfloat16 *__restrict__ bias,
+                                                           const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y,
+                                                           int M, int K, int bpr) {
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int row = blockIdx.x * 8 + warp, token = blockIdx.y;
+  if (row >= M) return;
+  x += size_t(token) * K;
+  float scale = scales[row];
+  float a0 = 0.f, a1 = 0.f;
+  for (int kb = lane; kb < bpr; kb += 32) {
+#pragma unroll
+    for (int quad = 0; quad < 4; ++quad) {
+      int qx = (quad & 1) * 2, qy = (quad >> 1) * 2;
+      // gather returns the 2x2 footprint as (w: x0y0, z: x1y0, x: x0y1, y: x1y1)
+      float4 v = tex2Dgather<float4>(texture, kb * 4 + qx + 1.f, row * 4 + qy + 1.f, 0);
+      int k = kb * 16 + qy * 4 + qx;
+      a0 = fmaf(__bfloat162float(__float2bfloat16(__fmul_rn(v.w, scale))), __bfloat162float(x[k]), a0);
+      a1 = fmaf(__bfloat162float(__float2bfloat16(__fmul_rn(v.z, scale))), __bfloat162float(x[k + 1]), a1);
+      a0 = fmaf(__bfloat162float(__float2bfloat16(__fmul_rn(v.x, scale))), __bfloat162float(x[k + 4]), a0);
+      a1 = fmaf(__bfloat162float(__float2bfloat16(__fmul_rn(v.y, scale))), __bfloat162float(x[k + 5]), a1);
+    }
+  }
+  float acc = a0 + a1;
+  for (int d = 16; d; d >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, d);
+  if (lane == 0) y[size_t(token) * M + row] = __float2bfloat16(acc + (bias ? __bfloat162float(bias[row]) : 0.f));
+}
+
+int launch_gemv_texture(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream) {
+  if (!h->texture) return fail(TX_ESTATE, "texture decode path selected but no texture object exists");
+  for (int t0 = 0; t0 < tokens; t0 += 65535) {
+    int n = std::min(tokens - t0, 65535);
+    dim3 grid((h->M + 7) / 8, n);
+    gemv_texture_kernel<<<grid, 256, 0, stream>>>(h->texture, h->scales, h->bias, x + size_t(t0) * h->K,
+                                                  y + size_t(t0) * h->M, h->M, h->K, h->blocks_per_row);
+    count_launch();
+  }
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Host launcher of the MMA GEMV
+// ------------------------------------------------------------------------------------------
+using GemvKernel = void (*)(const GemvParams);
+
+template <int NT, bool PRE>
+static GemvKernel pick_lookahead(int lookahead) {
+  switch (lookahead) {
+    case 1: return gemv_mma_kernel<1, NT, PRE>;
+    case 2: return gemv_mma_kernel<2, NT, PRE>;
+    case 3: return gemv_mma_kernel<3, NT, PRE>;
+    case 4: return gemv_mma_kernel<4, NT, PRE>;
+    case 6: return gemv_mma_kernel<6, NT, PRE>;
+    default: return gemv_mma_kernel<8, NT, PRE>;
+  }
+}
+
+static GemvKernel pick_kernel(int lookahead, int nt, bool pre) {
+  if (!pre) return pick_lookahead<1, false>(lookahead);
+  switch (nt) {
+    case 1: return pick_lookahead<1, true>(lookahead);
+    case 2: return pick_lookahead<2, true>(lookahead);
+    default: return pick_lookahead<4, true>(lookahead);
+  }
+}
+
+static size_t gemv_smem_bytes(int KP, int tokens) {
+  return size_t(kLutBytes) * 2 + 256 + size_t(tokens) * (size_t(KP) * 2 + kXsPad);
+}
+
+// Largest number of tokens one pass can take for this K (shared-memory bound), capped at 32.
+static int tokens_per_pass(int KP) {
+  size_t per_token = size_t(KP) * 2 + kXsPad;
+  size_t room = kSmemBudget - (size_t(kLutBytes) * 2 + 256);
+  int fit = int(std::min<size_t>(room / per_token, 8 * kMaxTokenTiles));
+  if (fit >= 8) fit = fit / 8 * 8;   // whole token tiles when possible
+  return fit;
+}
+
+struct GemvPlan {
+  GemvKernel kernel;
+  int nt, grid;
+  bool pre;
+  size_t smem;
+};
+
+static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan) {
+  Workspace *ws = workspace_for(h->device);
+  if (!ws) return TX_ECUDA;
+  int KP = h->KI * 128;
+  plan.nt = tokens <= 8 ? 1 : (tokens <= 16 ? 2 : 4);
+  // in-CTA activation conversion only while it stays a short prologue
+  plan.pre = !(tokens <= 2 && size_t(tokens) * h->K <= 36864);
+  plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre);
+  plan.smem = gemv_smem_bytes(KP, tokens);
+  // attribute + occupancy queries are cached per (device, kernel, shared bytes)
+  static std::mutex guard;
+  static std::map<std::tuple<int, const void *, size_t>, int> cache;
+  int per_sm = 0;
+  {
+    std::lock_guard<std::mutex> lock(guard);
+    auto key = std::make_tuple(h->device, reinterpret_cast<const void *>(plan.kernel), plan.smem);
+    auto hit = cache.find(key);
+    if (hit == cache.end()) {
+      TX_CUDA(cudaFuncSetAttribute(plan.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
+      TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, plan.kernel, kGemvThreads, plan.smem));
+      cache[key] = per_sm;
+    } else {
+      per_sm = hit->second;
+    }
+  }
+  if (per_sm < 1) return fail(TX_EINVAL, "decode GEMV does not fit in shared memory for this K");
+  per_sm = std::min(per_sm, 3);
+  long long units = (long long)h->MT * h->KI;
+  long long ctas = std::min<long long>((long long)ws->sm_count * per_sm, (units + kGemvWarps - 1) / kGemvWarps);
+  plan.grid = int(std::max<long long>(ctas, 1));
+  // every warp must own at least one unit so that tile segments map to consecutive warps
+  while ((long long)plan.grid * kGemvWarps > units && plan.grid > 1) --plan.grid;
+  return TX_OK;
+}
+
+int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream) {
+  Workspace *ws = workspace_for(h->device);
+  if (!ws) return TX_ECUDA;
+  int KP = h->KI * 128;
+  int per_pass = tokens_per_pass(KP);
+  if (per_pass < 1) return fail(TX_EINVAL, "K is too large for the decode GEMV's shared-memory staging");
+  for (int t0 = 0; t0 < tokens; t0 += per_pass) {
+    int n = std::min(per_pass, tokens - t0);
+    GemvPlan plan;
+    int rc = plan_gemv(h, n, plan);
+    if (rc != TX_OK) return rc;
+    long long units = (long long)h->MT * h->KI;
+    int total_warps = plan.grid * kGemvWarps;
+    if (units < total_warps) {  // tiny matrices: one CTA, fewer units than warps is handled by empty ranges
+      total_warps = int(std::max<long long>(units, 1));
+    }
+    GemvParams p{};
+    p.tiles = reinterpret_cast<const uint4 *>(h->tiles);
+    p.flags = h->unit_flags;
+    p.scales = h->scales;
+    p.bias = h->bias;
+    p.x = x + size_t(t0) * h->K;
+    p.y = y + size_t(t0) * h->M;
+    p.partials = ws->partials;
+    p.counters = ws->counters;
+    p.M = h->M;
+    p.K = h->K;
+    p.KI = h->KI;
+    p.T = n;
+    p.KP = KP;
+    p.units = units;
+    p.total_warps = total_warps;
+    if (size_t(total_warps) * 2 * plan.nt * 128 > ws->partial_floats || size_t(h->MT) > ws->counter_count)
+      return fail(TX_ESTATE, "split-K workspace is too small for this launch");
+    if (plan.pre) {
+      if (size_t(n) * KP > ws->xprep_halfs) return fail(TX_EINVAL, "tokens*K exceeds the activation scratch of the decode GEMV");
+      gemv_xprep_kernel<<<n, kGemvThreads, 0, stream>>>(p.x, ws->xprep, ws->xmul, h->K, KP);
+      count_launch();
+      p.xprep = ws->xprep;
+      p.xmul = ws->xmul;
+    }
+    plan.kernel<<<plan.grid, kGemvThreads, plan.smem, stream>>>(p);
+    count_launch();
+  }
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
+int gemv_kernel_info(int64_t out[9]) {
+  cudaFuncAttributes attributes{};
+  GemvKernel kernel = gemv_mma_kernel<2, 1, false>;
+  TX_CUDA(cudaFuncGetAttributes(&attributes, kernel));
+  TX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
+  int active = 0;
+  size_t smem = gemv_smem_bytes(4096, 1);
+  TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&active, kernel, kGemvThreads, smem));
+  out[0] = attributes.numRegs;
+  out[1] = int64_t(attributes.sharedSizeBytes);
+  out[2] = int64_t(attributes.localSizeBytes);
+  out[3] = attributes.maxThreadsPerBlock;
+  out[4] = int64_t(smem);
+  out[5] = 16;   // rows per unit
+  out[6] = 8;    // tokens per mma tile
+  out[7] = 128;  // columns per unit
+  out[8] = active;
+  return TX_OK;
+}
+
+}  // namespace tx

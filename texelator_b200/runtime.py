@@ -1,0 +1,399 @@
+"""Python operator surface of the BC4 weight-linear path.
+
+Mirrors ``texelator/runtime.py`` of the reference (``extension()`` :27-63,
+``TexelatorLinear`` :133-145, ``DecodeOnlyLinear`` :148-157, ``pack_entry`` :168-176,
+``pack_entry_handles`` :179-207, ``install`` :210-239, ``install_standalone``
+:242-263, ``free`` :266-274) with the same names, argument meaning and error
+behaviour, but the object returned by ``extension()`` drives the sm_100a C-ABI
+library ``texelator_b200/cuda/libtexelator_b200.so`` through ctypes instead of a
+pybind11 torch extension.  PyTorch is used for device memory and streams only.
+
+There is no CPU fallback: if the CUDA library is missing and cannot be built,
+``extension()`` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import gc
+import json
+import os
+from pathlib import Path
+
+import numpy as np
+import torch
+from torch import nn
+
+from .adapters import resolve_parent
+
+PACKAGE_ROOT = Path(__file__).resolve().parent
+LIBRARY_PATH = PACKAGE_ROOT / "cuda" / "libtexelator_b200.so"
+_EXTENSION = None
+PREFILL_THRESHOLD = int(os.environ.get("TEXELATOR_PREFILL_THRESHOLD", "16"))
+PREFILL_TILE_ROWS = int(os.environ.get("TEXELATOR_PREFILL_TILE_ROWS", "1024"))
+
+DTYPE_F16, DTYPE_BF16 = 0, 1
+DECODE_ALU_MMA, DECODE_ALU_EXACT, DECODE_TEXTURE = 0, 1, 2
+DEQUANT_PALETTE_F32, DEQUANT_SCALED_F32, DEQUANT_SCALED_BF16 = 0, 1, 2
+TX_EUNSUPPORTED = -3
+
+# every symbol include/texelator_b200.h declares: name -> (restype, argtypes)
+_u64, _i32, _i64p = ctypes.c_uint64, ctypes.c_int, ctypes.POINTER(ctypes.c_int64)
+_vp, _sz = ctypes.c_void_p, ctypes.c_size_t
+C_API = {
+    "tx_last_error": (ctypes.c_char_p, []),
+    "tx_runtime_info": (_i32, [_i32, _i64p]),
+    "tx_pack_encoded": (_i32, [_vp, _sz, _vp, _i32, _vp, _i32, _i32, ctypes.POINTER(_u64)]),
+    "tx_pack_encoded_shard": (_i32, [_vp, _sz, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32,
+                                     ctypes.POINTER(_u64)]),
+    "tx_linear": (_i32, [_u64, _vp, _vp, _i32, _i32, _vp]),
+    "tx_set_lookahead": (_i32, [_u64, _i32]),
+    "tx_set_prefill": (_i32, [_u64, _i32, _i32]),
+    "tx_set_prefill_backend": (_i32, [_u64, _i32]),
+    "tx_set_decode_path": (_i32, [_u64, _i32]),
+    "tx_handle_info": (_i32, [_u64, _i64p]),
+    "tx_kernel_info": (_i32, [_i32, _i64p]),
+    "tx_free": (_i32, [_u64]),
+    "tx_palette_probe": (_i32, [_i32, _vp]),
+    "tx_software_palette": (_i32, [_i32, _vp]),
+    "tx_dequant": (_i32, [_u64, _vp, _i32, _vp]),
+    "tx_unpack_blocks": (_i32, [_u64, _vp]),
+    "tx_launch_count": (ctypes.c_int64, []),
+}
+
+
+def load_library(path: Path | None = None) -> ctypes.CDLL:
+    """dlopen the C-ABI library and bind every declared symbol (raises if one is missing)."""
+    library = ctypes.CDLL(str(path or LIBRARY_PATH))
+    for name, (restype, argtypes) in C_API.items():
+        function = getattr(library, name)
+        function.restype = restype
+        function.argtypes = argtypes
+    return library
+
+
+class _Extension:
+    """The module-like object the reference gets from ``extension()``
+    (texelator/cuda/extension.cpp:27-48): same function names and semantics."""
+
+    def __init__(self, library: ctypes.CDLL):
+        self._lib = library
+        self._shapes: dict[int, tuple[int, int, int]] = {}   # handle -> (M, K, device)
+
+    # -- helpers -------------------------------------------------------------
+    def _check(self, status: int) -> None:
+        if status != 0:
+            message = self._lib.tx_last_error().decode(errors="replace")
+            raise RuntimeError(message or f"texelator_b200 call failed with status {status}")
+
+    @staticmethod
+    def _device_index(device: torch.device | int | None) -> int:
+        if device is None:
+            return torch.cuda.current_device()
+        if isinstance(device, int):
+            return device
+        return device.index if device.index is not None else torch.cuda.current_device()
+
+    # -- reference surface ---------------------------------------------------
+    def pack_encoded(self, blocks: torch.Tensor, scales: torch.Tensor, bias: torch.Tensor | None = None) -> int:
+        if blocks.is_cuda or blocks.dtype != torch.uint8 or not blocks.is_contiguous():
+            raise RuntimeError("blocks must be contiguous CPU uint8")
+        if scales.is_cuda or scales.dtype != torch.float32 or not scales.is_contiguous():
+            raise RuntimeError("scales must be contiguous CPU float32")
+        m = scales.numel()
+        device = torch.cuda.current_device()
+        bias_ptr, bias_dtype = self._bias_argument(bias, m, device)
+        handle = _u64(0)
+        self._check(self._lib.tx_pack_encoded(blocks.data_ptr(), blocks.numel(), scales.data_ptr(), m,
+                                              bias_ptr, bias_dtype, device, ctypes.byref(handle)))
+        k = 16 * (blocks.numel() // (8 * m))
+        self._shapes[handle.value] = (m, k, device)
+        return handle.value
+
+    def pack_encoded_shard(self, blocks: torch.Tensor, scales: torch.Tensor, m: int, k: int,
+                           rows: tuple[int, int], kblocks: tuple[int, int],
+                           bias: torch.Tensor | None = None) -> int:
+        """Tensor-parallel pack: rows ``[rows[0], rows[1])`` and 16-column blocks
+        ``[kblocks[0], kblocks[1])`` of a full ``m x k`` matrix (no reference counterpart)."""
+        if blocks.is_cuda or blocks.dtype != torch.uint8 or not blocks.is_contiguous():
+            raise RuntimeError("blocks must be contiguous CPU uint8")
+        if scales.is_cuda or scales.dtype != torch.float32 or not scales.is_contiguous():
+            raise RuntimeError("scales must be contiguous CPU float32")
+        device = torch.cuda.current_device()
+        bias_ptr, bias_dtype = self._bias_argument(bias, m, device)
+        handle = _u64(0)
+        self._check(self._lib.tx_pack_encoded_shard(blocks.data_ptr(), blocks.numel(), scales.data_ptr(), m, k,
+                                                    rows[0], rows[1], kblocks[0], kblocks[1], bias_ptr, bias_dtype,
+                                                    device, ctypes.byref(handle)))
+        self._shapes[handle.value] = (rows[1] - rows[0], 16 * (kblocks[1] - kblocks[0]), device)
+        return handle.value
+
+    @staticmethod
+    def _bias_argument(bias, m, device):
+        if bias is None or bias.numel() == 0:
+            return None, DTYPE_BF16
+        contiguous = bias.detach().contiguous()
+        if not contiguous.is_cuda or contiguous.dtype not in (torch.float16, torch.bfloat16) or contiguous.numel() != m:
+            raise RuntimeError("bias must be CUDA FP16 or BF16 [M]")
+        # keep the tensor alive until the (synchronous) copy inside the call is done
+        _Extension._bias_keepalive = contiguous
+        return contiguous.data_ptr(), (DTYPE_BF16 if contiguous.dtype == torch.bfloat16 else DTYPE_F16)
+
+    def linear(self, handle: int, x: torch.Tensor) -> torch.Tensor:
+        shape = self._shapes.get(handle)
+        if shape is None:
+            raise RuntimeError("null Texelator handle")
+        m, k, device = shape
+        if not x.is_cuda or x.dtype not in (torch.float16, torch.bfloat16) or not x.is_contiguous():
+            raise RuntimeError("input must be contiguous CUDA FP16 or BF16")
+        if x.size(-1) != k or x.get_device() != device:
+            raise RuntimeError("input shape/device mismatch")
+        tokens = x.numel() // k
+        y = torch.empty(x.shape[:-1] + (m,), dtype=x.dtype, device=x.device)
+        if tokens == 0:
+            return y
+        stream = torch.cuda.current_stream(device).cuda_stream
+        dtype = DTYPE_BF16 if x.dtype == torch.bfloat16 else DTYPE_F16
+        self._check(self._lib.tx_linear(handle, x.data_ptr(), y.data_ptr(), tokens, dtype, stream))
+        return y
+
+    def linear_out(self, handle: int, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        """``linear`` into a caller-provided output (static buffers for CUDA graphs)."""
+        m, k, device = self._shapes[handle]
+        tokens = x.numel() // k
+        if y.numel() != tokens * m or y.dtype != x.dtype or not y.is_contiguous() or not x.is_contiguous():
+            raise RuntimeError("input shape/device mismatch")
+        stream = torch.cuda.current_stream(device).cuda_stream
+        self._check(self._lib.tx_linear(handle, x.data_ptr(), y.data_ptr(), tokens, DTYPE_BF16, stream))
+        return y
+
+    def set_lookahead(self, handle: int, lookahead: int) -> None:
+        self._check(self._lib.tx_set_lookahead(handle, int(lookahead)))
+
+    def set_prefill(self, handle: int, threshold: int, tile_rows: int) -> None:
+        self._check(self._lib.tx_set_prefill(handle, int(threshold), int(tile_rows)))
+
+    def set_prefill_backend(self, handle: int, backend: int) -> None:
+        self._check(self._lib.tx_set_prefill_backend(handle, int(backend)))
+
+    def handle_info(self, handle: int) -> list[int]:
+        out = (ctypes.c_int64 * 7)()
+        self._check(self._lib.tx_handle_info(handle, out))
+        return list(out)
+
+    def kernel_info(self, backend: int) -> list[int]:
+        out = (ctypes.c_int64 * 9)()
+        self._check(self._lib.tx_kernel_info(int(backend), out))
+        return list(out)
+
+    # the reference exposes one info function per tile (extension.cpp:36-42)
+    def cutlass_texture_kernel_info(self) -> list[int]:
+        return self.kernel_info(5)
+
+    def cutlass_t1_kernel_info(self) -> list[int]:
+        return self.kernel_info(6)
+
+    def cutlass_t2_kernel_info(self) -> list[int]:
+        return self.kernel_info(7)
+
+    def cutlass_t3_kernel_info(self) -> list[int]:
+        return self.kernel_info(8)
+
+    def cutlass_smalln_kernel_info(self) -> list[int]:
+        return self.kernel_info(9)
+
+    def free(self, handle: int) -> None:
+        self._shapes.pop(handle, None)
+        self._check(self._lib.tx_free(handle))
+
+    def palette_probe(self) -> torch.Tensor:
+        """CPU float32 ``[65025, 8]``, row ``(e1+127)*255 + (e0+127)`` measured through a
+        signed-BC4 CUDA texture (texelator_cuda.cu:1540-1595).  Raises when the device has no
+        BC4 texture views."""
+        out = torch.empty((255 * 255, 8), dtype=torch.float32)
+        self._check(self._lib.tx_palette_probe(torch.cuda.current_device(), out.data_ptr()))
+        return out
+
+    # -- additions -----------------------------------------------------------
+    def software_palette(self) -> torch.Tensor:
+        """The same table produced by the library's ALU decoder."""
+        out = torch.empty((255 * 255, 8), dtype=torch.float32)
+        self._check(self._lib.tx_software_palette(torch.cuda.current_device(), out.data_ptr()))
+        return out
+
+    def texture_supported(self) -> bool:
+        return bool(self.runtime_info()[3])
+
+    def runtime_info(self, device: int | None = None) -> list[int]:
+        out = (ctypes.c_int64 * 4)()
+        self._check(self._lib.tx_runtime_info(self._device_index(device), out))
+        return list(out)
+
+    def set_decode_path(self, handle: int, path: int) -> None:
+        self._check(self._lib.tx_set_decode_path(handle, int(path)))
+
+    def dequant(self, handle: int, what: int = DEQUANT_SCALED_BF16) -> torch.Tensor:
+        m, k, device = self._shapes[handle]
+        dtype = torch.bfloat16 if what == DEQUANT_SCALED_BF16 else torch.float32
+        out = torch.empty((m, k), dtype=dtype, device=torch.device("cuda", device))
+        stream = torch.cuda.current_stream(device).cuda_stream
+        self._check(self._lib.tx_dequant(handle, out.data_ptr(), int(what), stream))
+        return out
+
+    def unpack_blocks(self, handle: int) -> torch.Tensor:
+        m, k, _ = self._shapes[handle]
+        out = torch.empty(m * k // 2, dtype=torch.uint8)
+        self._check(self._lib.tx_unpack_blocks(handle, out.data_ptr()))
+        return out
+
+    def launch_count(self) -> int:
+        return int(self._lib.tx_launch_count())
+
+
+def extension(verbose: bool = False):
+    """Load (building in-tree with nvcc if needed) the CUDA library.  Like the reference
+    (runtime.py:27-63) this raises instead of degrading when no native code is available;
+    ``TEXELATOR_DISABLE_JIT`` forbids the nvcc build."""
+    global _EXTENSION
+    if _EXTENSION is None:
+        if not LIBRARY_PATH.exists():
+            if os.environ.get("TEXELATOR_DISABLE_JIT", "").upper() in {"1", "ON", "YES", "TRUE"}:
+                raise RuntimeError(
+                    "the prebuilt Texelator CUDA library is unavailable and JIT compilation is disabled")
+            from .cuda.build import build
+            build(verbose=verbose)
+        try:
+            _EXTENSION = _Extension(load_library())
+        except (OSError, AttributeError) as error:
+            raise RuntimeError(f"the Texelator CUDA library could not be loaded: {error}") from error
+    return _EXTENSION
+
+
+def _linear_dispatch(handle: int, x: torch.Tensor) -> torch.Tensor:
+    # texelator/runtime.py:120-130 (the opt-in FP4 experiment is not part of this build)
+    return extension().linear(handle, x)
+
+
+class TexelatorLinear(nn.Module):
+    """texelator/runtime.py:133-145."""
+
+    def __init__(self, handles: list[int], bias: nn.Parameter | None = None):
+        super().__init__()
+        if not handles:
+            raise ValueError("TexelatorLinear requires at least one texture handle")
+        self.handles = list(handles)
+        self.bias = bias
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        contiguous = x.contiguous()
+        outputs = [_linear_dispatch(handle, contiguous) for handle in self.handles]
+        output = outputs[0] if len(outputs) == 1 else torch.cat(outputs, dim=-1)
+        return output if self.bias is None else output + self.bias
+
+
+class DecodeOnlyLinear(nn.Module):
+    """texelator/runtime.py:148-157."""
+
+    def __init__(self, original: nn.Module, quantized: nn.Module):
+        super().__init__()
+        self.original = original
+        self.quantized = quantized
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.numel() == x.shape[-1]:
+            return self.quantized(x)
+        return self.original(x)
+
+
+def _cpu_u8(path: Path) -> torch.Tensor:
+    return torch.from_numpy(np.fromfile(path, dtype=np.uint8).copy())
+
+
+def _cpu_f32(path: Path) -> torch.Tensor:
+    return torch.from_numpy(np.fromfile(path, dtype="<f4").copy())
+
+
+def pack_entry(weights: Path, entry: dict, bias: torch.Tensor | None = None, lookahead: int = 1) -> int:
+    """texelator/runtime.py:168-176."""
+    ext = extension()
+    handle = ext.pack_encoded(_cpu_u8(weights / entry["blocks_file"]), _cpu_f32(weights / entry["scales_file"]), bias)
+    ext.set_lookahead(handle, lookahead)
+    ext.set_prefill(handle, PREFILL_THRESHOLD, PREFILL_TILE_ROWS)
+    return handle
+
+
+def pack_entry_handles(weights: Path, entry: dict, bias: torch.Tensor | None = None, lookahead: int = 1,
+                       max_texture_rows: int = 32768) -> list[int]:
+    """Pack one matrix, splitting very tall outputs into independent handles
+    (texelator/runtime.py:179-207; the reference needs the split for the texture height limit,
+    it is kept so handle lists look the same)."""
+    m, k = int(entry["M"]), int(entry["K"])
+    if max_texture_rows <= 0:
+        raise ValueError("max_texture_rows must be positive")
+    row_bytes = (k // 16) * 8
+    raw_blocks = np.memmap(weights / entry["blocks_file"], dtype=np.uint8, mode="r", shape=(m, row_bytes))
+    raw_scales = np.memmap(weights / entry["scales_file"], dtype="<f4", mode="r", shape=(m,))
+    ext = extension()
+    handles: list[int] = []
+    try:
+        for start in range(0, m, max_texture_rows):
+            stop = min(start + max_texture_rows, m)
+            block_tensor = torch.from_numpy(np.ascontiguousarray(raw_blocks[start:stop]).reshape(-1))
+            scale_tensor = torch.from_numpy(np.ascontiguousarray(raw_scales[start:stop]))
+            handle = ext.pack_encoded(block_tensor, scale_tensor, bias[start:stop] if bias is not None else None)
+            ext.set_lookahead(handle, lookahead)
+            ext.set_prefill(handle, PREFILL_THRESHOLD, PREFILL_TILE_ROWS)
+            handles.append(handle)
+    except Exception:
+        free(handles)
+        raise
+    return handles
+
+
+def install(model: nn.Module, weights: Path, lookahead: int = 1, fp16_prefill: bool = False) -> list[int]:
+    """Replace the linears named in ``weights/metadata.json`` (texelator/runtime.py:210-239)."""
+    metadata = json.loads((weights / "metadata.json").read_text())
+    handles: list[int] = []
+    for entry in metadata["entries"]:
+        parent, child = resolve_parent(model, entry["module_name"])
+        original = getattr(parent, child)
+        device = original.weight.device
+        if device.type != "cuda":
+            raise RuntimeError(f"{entry['module_name']} is on {device}; selected linears must be CUDA resident")
+        bias = original.bias if getattr(original, "bias", None) is not None else None
+        with torch.cuda.device(device):
+            entry_handles = pack_entry_handles(weights, entry, bias=bias, lookahead=lookahead)
+        quantized = TexelatorLinear(entry_handles)
+        setattr(parent, child, DecodeOnlyLinear(original, quantized) if fp16_prefill else quantized)
+        handles.extend(entry_handles)
+        if not fp16_prefill:
+            del original
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
+    model._texelator_handles = handles
+    return handles
+
+
+def install_standalone(model: nn.Module, weights: Path, entries: list[dict], name_mapper, lookahead: int = 1) -> list[int]:
+    """Replace meta-initialised linears without dense source weights (texelator/runtime.py:242-263)."""
+    handles: list[int] = []
+    try:
+        for entry in entries:
+            parent, child = resolve_parent(model, name_mapper(entry["module_name"]))
+            original = getattr(parent, child)
+            entry_handles = pack_entry_handles(weights, entry, lookahead=lookahead)
+            setattr(parent, child, TexelatorLinear(entry_handles, bias=getattr(original, "bias", None)))
+            handles.extend(entry_handles)
+    except Exception:
+        free(handles)
+        raise
+    model._texelator_handles = handles
+    return handles
+
+
+def free(handles: list[int]) -> None:
+    """texelator/runtime.py:266-274."""
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    for handle in handles:
+        extension().free(handle)
