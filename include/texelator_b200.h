@@ -55,7 +55,9 @@ int tx_runtime_info(int device, int64_t out[4]);
 /* pack_encoded(blocks, scales, bias) -> handle: texelator_cuda.cu:1260-1327 (extension.cpp:28-29).
  * `blocks`: host, M * K/16 * 8 bytes, row-major BC4 blocks (encoder.py:105-117); `scales`: host,
  * M floats; `bias_dev`: optional device pointer to M elements of `bias_dtype` (copied).  K is
- * derived as 16 * nbytes / (8*M).  Copies are complete when the call returns. */
+ * derived as 16 * nbytes / (8*M).  Copies are complete when the call returns.  `blocks` and
+ * `scales` may also be device pointers (the copies use cudaMemcpyDefault), which lets a caller that
+ * encodes on the GPU pack without a round trip through host memory. */
 int tx_pack_encoded(const uint8_t *blocks, size_t nbytes, const float *scales, int M,
                     const void *bias_dev, int bias_dtype, int device, uint64_t *out_handle);
 

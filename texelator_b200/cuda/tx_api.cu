@@ -23,10 +23,8 @@ int fail(int code, const std::string &message) {
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
-// The scratch is sized once per device for the largest persistent grid this library launches:
-//   partial tiles : SMs * 3 CTAs * 8 warps * 2 segments * 4 token tiles * 128 floats
-//   counters      : one per 16-row tile, up to 2^20 output rows
-//   activations   : 32 tokens * 65536 columns of fp16
+// The scratch is sized once per device: 32 tokens * 65536 columns of scaled fp16 activations
+// for multi-token decode passes, plus their per-token multipliers.
 Workspace *workspace_for(int device) {
   std::lock_guard<std::mutex> lock(g_workspace_guard);
   auto found = g_workspaces.find(device);
@@ -36,12 +34,7 @@ Workspace *workspace_for(int device) {
   Workspace ws;
   cudaError_t status = cudaSetDevice(device);
   if (status == cudaSuccess) status = cudaDeviceGetAttribute(&ws.sm_count, cudaDevAttrMultiProcessorCount, device);
-  ws.partial_floats = size_t(ws.sm_count) * 3 * 8 * 2 * 4 * 128;
-  ws.counter_count = size_t(1) << 16;
   ws.xprep_halfs = size_t(32) * 65536;
-  if (status == cudaSuccess) status = cudaMalloc(&ws.partials, ws.partial_floats * sizeof(float));
-  if (status == cudaSuccess) status = cudaMalloc(&ws.counters, ws.counter_count * sizeof(unsigned));
-  if (status == cudaSuccess) status = cudaMemset(ws.counters, 0, ws.counter_count * sizeof(unsigned));
   if (status == cudaSuccess) status = cudaMalloc(&ws.xprep, ws.xprep_halfs * sizeof(__half));
   if (status == cudaSuccess) status = cudaMalloc(&ws.xmul, 64 * sizeof(float));
   cudaSetDevice(previous);
@@ -98,14 +91,16 @@ static int pack_common(const uint8_t *blocks, size_t src_pitch_blocks, const flo
   auto check = [&](cudaError_t s, const char *what) {
     if (s != cudaSuccess && rc == TX_OK) rc = fail(TX_ECUDA, std::string(what) + ": " + cudaGetErrorString(s));
   };
-  check(cudaMalloc(&h->tiles, units * kUnitBytes), "cudaMalloc(tiles)");
-  check(cudaMalloc(&h->unit_flags, units), "cudaMalloc(flags)");
+  check(cudaMalloc(&h->tiles, (units + kPadUnits) * kUnitBytes), "cudaMalloc(tiles)");
+  check(cudaMalloc(&h->unit_flags, units + kPadUnits), "cudaMalloc(flags)");
+  if (rc == TX_OK) check(cudaMemset(h->tiles + units * kUnitBytes, 0, size_t(kPadUnits) * kUnitBytes), "cudaMemset(pad)");
+  if (rc == TX_OK) check(cudaMemset(h->unit_flags + units, 0, kPadUnits), "cudaMemset(pad flags)");
   check(cudaMalloc(&h->scales, size_t(rows) * sizeof(float)), "cudaMalloc(scales)");
   check(cudaMalloc(&staging, size_t(rows) * bpr * 8), "cudaMalloc(staging)");
   if (rc == TX_OK)
-    check(cudaMemcpy2D(staging, size_t(bpr) * 8, blocks, src_pitch_blocks * 8, size_t(bpr) * 8, rows, cudaMemcpyHostToDevice),
+    check(cudaMemcpy2D(staging, size_t(bpr) * 8, blocks, src_pitch_blocks * 8, size_t(bpr) * 8, rows, cudaMemcpyDefault),
           "cudaMemcpy2D(blocks)");
-  if (rc == TX_OK) check(cudaMemcpy(h->scales, scales, size_t(rows) * sizeof(float), cudaMemcpyHostToDevice), "cudaMemcpy(scales)");
+  if (rc == TX_OK) check(cudaMemcpy(h->scales, scales, size_t(rows) * sizeof(float), cudaMemcpyDefault), "cudaMemcpy(scales)");
   if (rc == TX_OK) rc = launch_retile(staging, h, 0);
   if (rc == TX_OK && bias_dev) {
     check(cudaMalloc(&h->bias, size_t(rows) * 2), "cudaMalloc(bias)");

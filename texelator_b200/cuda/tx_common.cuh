@@ -31,6 +31,7 @@ namespace tx {
 constexpr int kUnitRows = 16;
 constexpr int kUnitBlocks = 8;
 constexpr int kUnitBytes = 1024;
+constexpr int kPadUnits = 8;   // readable units behind the payload (unguarded prefetch of the decode GEMV)
 constexpr unsigned long long kPadBlock = 0x0000000000000001ull;  // e0=1, e1=0, selectors 0
 
 __host__ __device__ inline size_t tiled_block_offset(int row, int kb, int KI) {
@@ -58,10 +59,6 @@ struct Handle {
 
 // Per-device scratch shared by every handle of the process on that device.
 struct Workspace {
-  float *partials = nullptr;      // split-K partial tiles
-  size_t partial_floats = 0;
-  unsigned *counters = nullptr;   // one arrival counter per row tile, all zero between launches
-  size_t counter_count = 0;
   __half *xprep = nullptr;        // scaled fp16 activations of multi-token decode passes
   size_t xprep_halfs = 0;
   float *xmul = nullptr;          // per-token multipliers (64 floats)

@@ -1,10 +1,9 @@
 // Decode GEMV for tokens < prefill_threshold (reference: texelator_bc4_bf16_kernel,
 // texelator/cuda/texelator_cuda.cu:141-199, one warp per output row through the texture unit).
 //
-// B200 design.  The kernel is a persistent stream-K sweep over 1 KiB units (16 rows x 128
-// columns) of the tiled BC4 payload.  Every warp owns a contiguous range of units, keeps LOOKAHEAD
-// units in flight as 128-bit loads, and turns each unit into eight mma.sync m16n8k16 A fragments
-// entirely in registers:
+// B200 design.  A persistent CTA walks 16-row tiles of the tiled BC4 payload; its eight warps split
+// the tile's 1 KiB units (16 rows x 128 columns) round-robin, keep LOOKAHEAD units in flight as
+// 128-bit loads, and turn each unit into eight mma.sync m16n8k16 A fragments entirely in registers:
 //
 //   * per block, the two int8 endpoints become fp16x2 constants  base = 7*e0, delta = e1-e0
 //     (byte-permute into the fp16 "1024+u" encoding, then one HSUB2 / HFMA2; exact integers);
@@ -21,10 +20,8 @@
 // Blocks in the low palette mode (e0 <= e1) are rare; units that contain one are flagged at pack
 // time and take a warp-uniform slow path with per-weight arithmetic.
 //
-// Row tiles whose K range is split over several warps are combined through a per-device scratch
-// buffer: every contributor stores its fp32 partial tile, and the last one to arrive (an atomic
-// counter per row tile) sums all partials in warp order, so results are deterministic.  There is
-// no spin-wait anywhere in this file.
+// The warps of a CTA combine their fp32 partial tiles through shared memory in warp order, so
+// results are deterministic; the only waits in this file are CTA barriers.
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -49,12 +46,8 @@ struct GemvParams {
   __nv_bfloat16 *y;         // [T, M]
   const __half *xprep;      // [T, KP] pre-scaled fp16 activations (PRE) or null
   const float *xmul;        // [T] 2^s/889 per token (PRE)
-  float *partials;
-  unsigned *counters;
-  int M, K, KI, T;
+  int M, K, KI, T, MT;
   int KP;                   // KI * 128
-  long long units;          // MT * KI
-  int total_warps;
 };
 
 __device__ __forceinline__ unsigned lds32(unsigned addr) {
@@ -75,13 +68,19 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
 }
 __device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                         unsigned b0, unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ unsigned hfma2_u(unsigned a, unsigned b, unsigned c) {
   unsigned d;
   asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// (a & mask) | c as one LOP3
+__device__ __forceinline__ unsigned and_or(unsigned a, unsigned mask, unsigned c) {
+  unsigned d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(c));
   return d;
 }
 __device__ __forceinline__ unsigned hsub2_u(unsigned a, unsigned b) {
@@ -108,13 +107,13 @@ __device__ __forceinline__ void decode_block_fast(unsigned lo, unsigned hi, unsi
   f[7] = hi >> 19;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    unsigned g2 = lds32((f[i] & 0x1F80u) | lut_lane);
+    unsigned g2 = lds32(and_or(f[i], 0x1F80u, lut_lane));
     a[i] = hfma2_u(g2, delta, base);
   }
 }
 
 // Generic path: any mode, per-weight fp32 arithmetic, value = 889 * palette rounded to fp16.
-__device__ __noinline__ void decode_block_slow(unsigned lo, unsigned hi, unsigned (&a)[8]) {
+__device__ __forceinline__ void decode_block_slow(unsigned lo, unsigned hi, unsigned (&a)[8]) {
   unsigned long long block = (unsigned long long)lo | ((unsigned long long)hi << 32);
   int e0 = block_e0(block), e1 = block_e1(block);
 #pragma unroll
@@ -200,56 +199,56 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const __nv_bfl
     dst[i] = i < chunks ? convert_chunk(src[i], mult) : make_uint4(0, 0, 0, 0);
 }
 
-template <int NT>
-__device__ __forceinline__ void store_tile(const GemvParams &p, const float (&acc)[NT][4], const float *tokmul, int rt, int lane) {
-  int g = lane >> 2, t = lane & 3;
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    int row = rt * 16 + half * 8 + g;
-    if (row >= p.M) continue;
-    float scale = p.scales[row];
-    float bias = p.bias ? __bfloat162float(p.bias[row]) : 0.0f;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        int tok = nt * 8 + 2 * t + q;
-        if (tok < p.T) p.y[size_t(tok) * p.M + row] = __float2bfloat16(fmaf(acc[nt][half * 2 + q], scale * tokmul[tok], bias));
-      }
-  }
-}
-
+// ------------------------------------------------------------------------------------------
+// Decode GEMV, one 16-row tile per CTA iteration.  A persistent CTA walks row tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ...; its warps split the tile's column units round-robin
+// (unit ki = warp, warp + WS, ...), keep LOOKAHEAD units in flight across tile boundaries, and
+// combine their fp32 partial tiles through shared memory (double-buffered, one named barrier per
+// tile).  No global scratch, no atomics, deterministic summation order.
+// ------------------------------------------------------------------------------------------
 template <int LOOKAHEAD, int NT, bool PRE>
-__global__ void __launch_bounds__(kGemvThreads, PRE || NT > 1 ? 1 : 2) gemv_mma_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGemvThreads, (NT == 1 && LOOKAHEAD <= 2) ? 3 : (NT <= 2 ? 2 : 1))
+gemv_tile_kernel(const GemvParams p) {
   extern __shared__ uint8_t smem_raw[];
   const unsigned sbase = unsigned(__cvta_generic_to_shared(smem_raw));
   const unsigned lut_s = (sbase + kLutBytes - 1) & ~unsigned(kLutBytes - 1);
   uint8_t *lut_g = smem_raw + (lut_s - sbase);
-  float *tokmul = reinterpret_cast<float *>(lut_g + kLutBytes);  // 32 floats
+  float *tokmul = reinterpret_cast<float *>(lut_g + kLutBytes);           // 32 floats
   unsigned *red = reinterpret_cast<unsigned *>(lut_g + kLutBytes + 128);  // 8 words
-  uint8_t *xs_g = lut_g + kLutBytes + 256;
-  const unsigned xs_s = lut_s + kLutBytes + 256;
+  uint4 *zero_g = reinterpret_cast<uint4 *>(lut_g + kLutBytes + 256);     // 256 zero bytes
+  float *part_g = reinterpret_cast<float *>(lut_g + kLutBytes + 512);     // [2][8 warps][NT*128] partial tiles
+  constexpr int kPartBytes = 2 * kGemvWarps * NT * 128 * 4;
+  uint8_t *xs_g = lut_g + kLutBytes + 512 + kPartBytes;
+  const unsigned zero_s = lut_s + kLutBytes + 256;
+  const unsigned xs_s = lut_s + kLutBytes + 512 + kPartBytes;
   const unsigned xs_stride = unsigned(p.KP) * 2 + kXsPad;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
+  const int KI = p.KI, MT = p.MT;
+  const int WS = KI < kGemvWarps ? KI : kGemvWarps;   // warps that own column units
+  const bool worker = warp < WS;
 
-  // -- this warp's contiguous unit range (stream-K) and the first loads, issued before anything else
-  const long long gw = (long long)blockIdx.x * kGemvWarps + warp;
-  const bool has_work = gw < p.total_warps;
-  const long long u0 = has_work ? p.units * gw / p.total_warps : 0;
-  const long long u1 = has_work ? p.units * (gw + 1) / p.total_warps : 0;
+  // -- first loads, issued before anything else.  Prefetch addresses past the last tile fall back
+  //    to the first unit (valid memory, never consumed).
+  int ptile = blockIdx.x, pk = warp;
   uint4 pend[LOOKAHEAD][2];
   unsigned pflag[LOOKAHEAD];
-  const uint4 *src = p.tiles + u0 * 64 + lane;
-#pragma unroll
-  for (int i = 0; i < LOOKAHEAD; ++i) {
-    if (u0 + i < u1) {
-      pend[i][0] = ldg_stream(src + size_t(i) * 64);
-      pend[i][1] = ldg_stream(src + size_t(i) * 64 + 32);
-      pflag[i] = p.flags[u0 + i];
+  auto prefetch = [&](int slot) {
+    const bool live = worker && ptile < MT;
+    const long long unit = live ? (long long)ptile * KI + pk : 0;
+    const uint4 *src = p.tiles + unit * 64 + lane;
+    pend[slot][0] = ldg_stream(src);
+    pend[slot][1] = ldg_stream(src + 32);
+    pflag[slot] = p.flags[unit];
+    pk += WS;
+    if (pk >= KI) {
+      pk = warp;
+      ptile += gridDim.x;
     }
-  }
+  };
+#pragma unroll
+  for (int i = 0; i < LOOKAHEAD; ++i) prefetch(i);
 
   // -- selector-pair table: entry idx holds fp16x2 (g(idx & 7), g(idx >> 3)), replicated per lane
   for (int i = tid; i < 64 * 32; i += kGemvThreads) {
@@ -258,6 +257,7 @@ __global__ void __launch_bounds__(kGemvThreads, PRE || NT > 1 ? 1 : 2) gemv_mma_
     float g1 = s1 == 0 ? 0.f : (s1 == 1 ? 7.f : float(s1 - 1));
     reinterpret_cast<__half2 *>(lut_g)[i] = __floats2half2_rn(g0, g1);
   }
+  if (tid < 16) zero_g[tid] = make_uint4(0, 0, 0, 0);
 
   // -- activations -> fp16 in shared memory
   const int chunks = p.K / 8, padded = p.KP / 8;
@@ -291,45 +291,57 @@ __global__ void __launch_bounds__(kGemvThreads, PRE || NT > 1 ? 1 : 2) gemv_mma_
     }
   }
   __syncthreads();
-  if (u0 >= u1) return;
+  if (!worker || int(blockIdx.x) >= MT) return;
 
   const unsigned lut_lane = lut_s + lane * 4;
-  // shared address of this lane's activations for token tile 0 (token g); inactive lanes feed zeros
-  unsigned xs_lane[NT];
-  bool tok_ok[NT];
+  // shared address of this lane's activations per token tile (token = 8*nt + g); lanes whose token
+  // does not exist read a block of zeros instead and never advance
+  unsigned xs_lane[NT], xs_step[NT];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
-    tok_ok[nt] = nt * 8 + g < p.T;
-    xs_lane[nt] = xs_s + unsigned(nt * 8 + g) * xs_stride + t * 32;
+    bool ok = nt * 8 + g < p.T;
+    xs_lane[nt] = ok ? xs_s + unsigned(nt * 8 + g) * xs_stride + t * 32 : zero_s + t * 32;
+    xs_step[nt] = ok ? 0xffffffffu : 0u;
   }
 
-  float acc[NT][4];
+  // output elements this thread finalises: e = wtid + j*workers, e = (nt*4 + qd)*32 + lane'
+  const int workers = WS * 32;
+  constexpr int kElems = NT * 128;
+  constexpr int kPerThread = (kElems + 31) / 32;   // upper bound (one worker warp)
+  float row_scale[kPerThread], row_bias[kPerThread];
+  auto load_row_constants = [&](int rt) {
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {
+      int e = tid + j * workers;
+      int row = rt * 16 + ((e >> 6) & 1) * 8 + ((e & 31) >> 2);
+      bool ok = e < kElems && row < p.M;
+      row_scale[j] = ok ? p.scales[row] : 0.f;
+      row_bias[j] = ok && p.bias ? __bfloat162float(p.bias[row]) : 0.f;
+    }
+  };
+
+  // two independent accumulator chains halve the mma latency chain
+  float acc[NT][4], acc2[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-    for (int q = 0; q < 4; ++q) acc[nt][q] = 0.f;
+    for (int q = 0; q < 4; ++q) acc[nt][q] = acc2[nt][q] = 0.f;
 
-  int rt = int(u0 / p.KI), ki = int(u0 % p.KI);
-  int seg_first = ki;
-  long long u = u0;
-  while (u < u1) {
+  int tile = blockIdx.x, ki = warp, buf = 0;
+  unsigned xoff = unsigned(warp) * 256;
+  const unsigned xoff_step = unsigned(WS) * 256;
+  load_row_constants(tile);
+  while (true) {
 #pragma unroll
     for (int slot = 0; slot < LOOKAHEAD; ++slot) {
-      if (u >= u1) break;
-      uint4 q = pend[slot][0], r = pend[slot][1];
-      unsigned flag = pflag[slot];
-      if (u + LOOKAHEAD < u1) {
-        const uint4 *next = p.tiles + (u + LOOKAHEAD) * 64 + lane;
-        pend[slot][0] = ldg_stream(next);
-        pend[slot][1] = ldg_stream(next + 32);
-        pflag[slot] = p.flags[u + LOOKAHEAD];
-      }
+      const uint4 q = pend[slot][0], r = pend[slot][1];
+      const unsigned flag = pflag[slot];
+      prefetch(slot);
       // ---- one unit: blocks (ki*8 + t) [sub 0] and (ki*8 + 4 + t) [sub 1] of rows g and g+8
-      const unsigned xoff = unsigned(ki) * 256;
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
-        unsigned qlo = sub ? q.z : q.x, qhi = sub ? q.w : q.y;
-        unsigned rlo = sub ? r.z : r.x, rhi = sub ? r.w : r.y;
+        const unsigned qlo = sub ? q.z : q.x, qhi = sub ? q.w : q.y;
+        const unsigned rlo = sub ? r.z : r.x, rhi = sub ? r.w : r.y;
         unsigned aq[8], ar[8];
         if (flag) {
           if (block_is_low(qlo)) decode_block_slow(qlo, qhi, aq); else decode_block_fast(qlo, qhi, lut_lane, aq);
@@ -340,68 +352,47 @@ __global__ void __launch_bounds__(kGemvThreads, PRE || NT > 1 ? 1 : 2) gemv_mma_
         }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          uint4 b0 = make_uint4(0, 0, 0, 0), b1 = make_uint4(0, 0, 0, 0);
-          if (tok_ok[nt]) {
-            b0 = lds128(xs_lane[nt] + xoff + sub * 128);
-            b1 = lds128(xs_lane[nt] + xoff + sub * 128 + 16);
-          }
+          const unsigned xa = xs_lane[nt] + (xoff & xs_step[nt]) + sub * 128;
+          const uint4 b0 = lds128(xa), b1 = lds128(xa + 16);
           mma_f16(acc[nt], aq[0], ar[0], aq[1], ar[1], b0.x, b0.y);
-          mma_f16(acc[nt], aq[2], ar[2], aq[3], ar[3], b0.z, b0.w);
+          mma_f16(acc2[nt], aq[2], ar[2], aq[3], ar[3], b0.z, b0.w);
           mma_f16(acc[nt], aq[4], ar[4], aq[5], ar[5], b1.x, b1.y);
-          mma_f16(acc[nt], aq[6], ar[6], aq[7], ar[7], b1.z, b1.w);
+          mma_f16(acc2[nt], aq[6], ar[6], aq[7], ar[7], b1.z, b1.w);
         }
       }
-      // ---- end of a row tile segment?
-      if (ki == p.KI - 1 || u == u1 - 1) {
-        bool whole = seg_first == 0 && ki == p.KI - 1;
-        if (whole) {
-          store_tile<NT>(p, acc, tokmul, rt, lane);
-        } else {
-          // partial segment: slot 0 if this warp's range starts inside the tile, else slot 1
-          int which = u0 >= (long long)rt * p.KI ? 0 : 1;
-          float *mine = p.partials + (size_t(gw) * 2 + which) * (NT * 128);
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int qd = 0; qd < 4; ++qd) mine[(nt * 4 + qd) * 32 + lane] = acc[nt][qd];
-          __threadfence();
-          __syncwarp();
-          long long first_unit = (long long)rt * p.KI, last_unit = first_unit + p.KI - 1;
-          long long wf = ((first_unit + 1) * p.total_warps - 1) / p.units;
-          long long wl = ((last_unit + 1) * p.total_warps - 1) / p.units;
-          unsigned arrived = 0;
-          if (lane == 0) arrived = atomicAdd(&p.counters[rt], 1u);
-          arrived = __shfl_sync(0xffffffffu, arrived, 0);
-          if (arrived == unsigned(wl - wf)) {
-            __threadfence();
-            float sum[NT][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-              for (int qd = 0; qd < 4; ++qd) sum[nt][qd] = 0.f;
-            for (long long w = wf; w <= wl; ++w) {
-              long long ws = p.units * w / p.total_warps;
-              int wslot = ws >= first_unit ? 0 : 1;
-              const float *theirs = p.partials + (size_t(w) * 2 + wslot) * (NT * 128);
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int qd = 0; qd < 4; ++qd) sum[nt][qd] += __ldcg(theirs + (nt * 4 + qd) * 32 + lane);
-            }
-            store_tile<NT>(p, sum, tokmul, rt, lane);
-            if (lane == 0) p.counters[rt] = 0;   // ready for the next launch
-          }
-        }
+      ki += WS;
+      xoff += xoff_step;
+      if (ki >= KI) {
+        // ---- this warp's share of the tile is done: publish the partial, combine, store
+        float *mine = part_g + (buf * kGemvWarps + warp) * kElems + lane;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-          for (int qd = 0; qd < 4; ++qd) acc[nt][qd] = 0.f;
-        seg_first = 0;   // every later segment of this warp starts at the first column unit
-      }
-      ++u;
-      if (++ki == p.KI) {
-        ki = 0;
-        ++rt;
+          for (int qd = 0; qd < 4; ++qd) {
+            mine[(nt * 4 + qd) * 32] = acc[nt][qd] + acc2[nt][qd];
+            acc[nt][qd] = acc2[nt][qd] = 0.f;
+          }
+        asm volatile("bar.sync 1, %0;" ::"r"(workers) : "memory");
+#pragma unroll
+        for (int j = 0; j < kPerThread; ++j) {
+          const int e = tid + j * workers;
+          if (e < kElems) {
+            const float *src = part_g + buf * kGemvWarps * kElems + e;
+            float sum = 0.f;
+            for (int w = 0; w < WS; ++w) sum += src[w * kElems];
+            const int c = e >> 5, ln = e & 31;
+            const int row = tile * 16 + ((c >> 1) & 1) * 8 + (ln >> 2);
+            const int tok = (c >> 2) * 8 + 2 * (ln & 3) + (c & 1);
+            if (row < p.M && tok < p.T)
+              p.y[size_t(tok) * p.M + row] = __float2bfloat16(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j]));
+          }
+        }
+        buf ^= 1;
+        tile += gridDim.x;
+        if (tile >= MT) return;
+        ki = warp;
+        xoff = unsigned(warp) * 256;
+        load_row_constants(tile);
       }
     }
   }
@@ -504,12 +495,12 @@ using GemvKernel = void (*)(const GemvParams);
 template <int NT, bool PRE>
 static GemvKernel pick_lookahead(int lookahead) {
   switch (lookahead) {
-    case 1: return gemv_mma_kernel<1, NT, PRE>;
-    case 2: return gemv_mma_kernel<2, NT, PRE>;
-    case 3: return gemv_mma_kernel<3, NT, PRE>;
-    case 4: return gemv_mma_kernel<4, NT, PRE>;
-    case 6: return gemv_mma_kernel<6, NT, PRE>;
-    default: return gemv_mma_kernel<8, NT, PRE>;
+    case 1: return gemv_tile_kernel<1, NT, PRE>;
+    case 2: return gemv_tile_kernel<2, NT, PRE>;
+    case 3: return gemv_tile_kernel<3, NT, PRE>;
+    case 4: return gemv_tile_kernel<4, NT, PRE>;
+    case 6: return gemv_tile_kernel<6, NT, PRE>;
+    default: return gemv_tile_kernel<8, NT, PRE>;
   }
 }
 
@@ -522,17 +513,20 @@ static GemvKernel pick_kernel(int lookahead, int nt, bool pre) {
   }
 }
 
-static size_t gemv_smem_bytes(int KP, int tokens) {
-  return size_t(kLutBytes) * 2 + 256 + size_t(tokens) * (size_t(KP) * 2 + kXsPad);
+static size_t gemv_smem_bytes(int KP, int tokens, int nt) {
+  // alignment slack + table, 512 bytes of small arrays, double-buffered partial tiles, activations
+  return size_t(kLutBytes) * 2 + 512 + size_t(2 * kGemvWarps * 128 * 4) * nt + size_t(tokens) * (size_t(KP) * 2 + kXsPad);
 }
+
+static int token_tiles(int tokens) { return tokens <= 8 ? 1 : (tokens <= 16 ? 2 : 4); }
 
 // Largest number of tokens one pass can take for this K (shared-memory bound), capped at 32.
 static int tokens_per_pass(int KP) {
-  size_t per_token = size_t(KP) * 2 + kXsPad;
-  size_t room = kSmemBudget - (size_t(kLutBytes) * 2 + 256);
-  int fit = int(std::min<size_t>(room / per_token, 8 * kMaxTokenTiles));
-  if (fit >= 8) fit = fit / 8 * 8;   // whole token tiles when possible
-  return fit;
+  int best = 0;
+  for (int tokens = 1; tokens <= 8 * kMaxTokenTiles; ++tokens)
+    if (gemv_smem_bytes(KP, tokens, token_tiles(tokens)) <= kSmemBudget) best = tokens;
+  if (best >= 8) best = best / 8 * 8;   // whole token tiles when possible
+  return best;
 }
 
 struct GemvPlan {
@@ -546,11 +540,11 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan) {
   Workspace *ws = workspace_for(h->device);
   if (!ws) return TX_ECUDA;
   int KP = h->KI * 128;
-  plan.nt = tokens <= 8 ? 1 : (tokens <= 16 ? 2 : 4);
+  plan.nt = token_tiles(tokens);
   // in-CTA activation conversion only while it stays a short prologue
   plan.pre = !(tokens <= 2 && size_t(tokens) * h->K <= 36864);
   plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre);
-  plan.smem = gemv_smem_bytes(KP, tokens);
+  plan.smem = gemv_smem_bytes(KP, tokens, plan.nt);
   // attribute + occupancy queries are cached per (device, kernel, shared bytes)
   static std::mutex guard;
   static std::map<std::tuple<int, const void *, size_t>, int> cache;
@@ -568,12 +562,8 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan) {
     }
   }
   if (per_sm < 1) return fail(TX_EINVAL, "decode GEMV does not fit in shared memory for this K");
-  per_sm = std::min(per_sm, 3);
-  long long units = (long long)h->MT * h->KI;
-  long long ctas = std::min<long long>((long long)ws->sm_count * per_sm, (units + kGemvWarps - 1) / kGemvWarps);
-  plan.grid = int(std::max<long long>(ctas, 1));
-  // every warp must own at least one unit so that tile segments map to consecutive warps
-  while ((long long)plan.grid * kGemvWarps > units && plan.grid > 1) --plan.grid;
+  // persistent CTAs: one resident wave, each walking row tiles with stride gridDim.x
+  plan.grid = std::max(1, std::min(h->MT, ws->sm_count * std::min(per_sm, 3)));
   return TX_OK;
 }
 
@@ -588,11 +578,6 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
     GemvPlan plan;
     int rc = plan_gemv(h, n, plan);
     if (rc != TX_OK) return rc;
-    long long units = (long long)h->MT * h->KI;
-    int total_warps = plan.grid * kGemvWarps;
-    if (units < total_warps) {  // tiny matrices: one CTA, fewer units than warps is handled by empty ranges
-      total_warps = int(std::max<long long>(units, 1));
-    }
     GemvParams p{};
     p.tiles = reinterpret_cast<const uint4 *>(h->tiles);
     p.flags = h->unit_flags;
@@ -600,18 +585,14 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
     p.bias = h->bias;
     p.x = x + size_t(t0) * h->K;
     p.y = y + size_t(t0) * h->M;
-    p.partials = ws->partials;
-    p.counters = ws->counters;
     p.M = h->M;
     p.K = h->K;
     p.KI = h->KI;
+    p.MT = h->MT;
     p.T = n;
     p.KP = KP;
-    p.units = units;
-    p.total_warps = total_warps;
-    if (size_t(total_warps) * 2 * plan.nt * 128 > ws->partial_floats || size_t(h->MT) > ws->counter_count)
-      return fail(TX_ESTATE, "split-K workspace is too small for this launch");
     if (plan.pre) {
+      // scaled fp16 activations go through the per-device scratch (one pre-pass CTA per token)
       if (size_t(n) * KP > ws->xprep_halfs) return fail(TX_EINVAL, "tokens*K exceeds the activation scratch of the decode GEMV");
       gemv_xprep_kernel<<<n, kGemvThreads, 0, stream>>>(p.x, ws->xprep, ws->xmul, h->K, KP);
       count_launch();
@@ -627,11 +608,11 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
 
 int gemv_kernel_info(int64_t out[9]) {
   cudaFuncAttributes attributes{};
-  GemvKernel kernel = gemv_mma_kernel<2, 1, false>;
+  GemvKernel kernel = gemv_tile_kernel<2, 1, false>;
   TX_CUDA(cudaFuncGetAttributes(&attributes, kernel));
   TX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
   int active = 0;
-  size_t smem = gemv_smem_bytes(4096, 1);
+  size_t smem = gemv_smem_bytes(4096, 1, 1);
   TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&active, kernel, kGemvThreads, smem));
   out[0] = attributes.numRegs;
   out[1] = int64_t(attributes.sharedSizeBytes);

@@ -63,7 +63,7 @@ C_API = {
 
 def load_library(path: Path | None = None) -> ctypes.CDLL:
     """dlopen the C-ABI library and bind every declared symbol (raises if one is missing)."""
-    library = ctypes.CDLL(str(path or LIBRARY_PATH))
+    library = ctypes.CDLL(str(path or os.environ.get("TEXELATOR_B200_LIBRARY") or LIBRARY_PATH))
     for name, (restype, argtypes) in C_API.items():
         function = getattr(library, name)
         function.restype = restype
@@ -107,6 +107,23 @@ class _Extension:
                                               bias_ptr, bias_dtype, device, ctypes.byref(handle)))
         k = 16 * (blocks.numel() // (8 * m))
         self._shapes[handle.value] = (m, k, device)
+        return handle.value
+
+    def pack_encoded_device(self, blocks: torch.Tensor, scales: torch.Tensor, bias: torch.Tensor | None = None) -> int:
+        """``pack_encoded`` for blocks/scales that already live on the current CUDA device (an
+        encoder that runs on the GPU); same layout and semantics otherwise."""
+        if not blocks.is_cuda or blocks.dtype != torch.uint8 or not blocks.is_contiguous():
+            raise RuntimeError("blocks must be contiguous CUDA uint8")
+        if not scales.is_cuda or scales.dtype != torch.float32 or not scales.is_contiguous():
+            raise RuntimeError("scales must be contiguous CUDA float32")
+        m = scales.numel()
+        device = blocks.get_device()
+        torch.cuda.current_stream(device).synchronize()
+        bias_ptr, bias_dtype = self._bias_argument(bias, m, device)
+        handle = _u64(0)
+        self._check(self._lib.tx_pack_encoded(blocks.data_ptr(), blocks.numel(), scales.data_ptr(), m,
+                                              bias_ptr, bias_dtype, device, ctypes.byref(handle)))
+        self._shapes[handle.value] = (m, 16 * (blocks.numel() // (8 * m)), device)
         return handle.value
 
     def pack_encoded_shard(self, blocks: torch.Tensor, scales: torch.Tensor, m: int, k: int,
