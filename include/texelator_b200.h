@@ -114,6 +114,12 @@ int tx_dequant(uint64_t handle, void *out, int what, void *stream);
  * (round-trip check of the packed copy). `out_host` holds M*K/2 bytes. */
 int tx_unpack_blocks(uint64_t handle, uint8_t *out_host);
 
+/* New: device status word.  Kernels never spin without a limit; when a bounded wait of the tensor-core
+ * prefill kernel runs out it records a positive code (1..5 = producer, TMA, A-ready, X-ready,
+ * accumulator wait) here and returns early.  Synchronises the device; returns the code (0 = healthy)
+ * or a negative TX_E* value; `clear` resets it. */
+int tx_kernel_status(int device, int clear);
+
 /* Number of this library's kernels launched by the calling process since load (all threads). */
 int64_t tx_launch_count(void);
 

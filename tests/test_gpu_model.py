@@ -1,0 +1,49 @@
+"""Model-level parity on a GPU: BC4 decoder vs the same model with dequantised dense weights."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def toy():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from texelator_b200.modeling import CONFIGS, BC4Decoder
+    model = BC4Decoder(CONFIGS["toy"], "cuda:0", max_len=96, seed=3, keep_dense=True)
+    yield model
+    model.free()
+
+
+def _cosine(a, b):
+    return float(torch.nn.functional.cosine_similarity(a.float().reshape(1, -1), b.float().reshape(1, -1)).item())
+
+
+def test_prefill_hidden_state_cosine(toy):
+    ids = torch.randint(0, toy.config.vocab, (40,), generator=torch.Generator().manual_seed(0))
+    for backend in (0, 5):
+        for h in toy.handles:
+            toy.ext.set_prefill_backend(h, backend)
+        got = toy.prefill(ids)
+        ref = toy.prefill(ids, dense=True)
+        assert _cosine(got, ref) >= 0.999, backend      # final hidden-state gate of the operator
+
+
+def test_decode_graph_matches_eager_and_dense(toy):
+    ids = torch.randint(0, toy.config.vocab, (24,), generator=torch.Generator().manual_seed(1))
+    toy.prefill(ids)
+    toy.tok.fill_(int(ids[-1]))
+    state = (toy.tok.clone(), toy.pos.clone(), toy.mask.clone())
+    toy.decode_eager()
+    eager_hidden, eager_tok = toy.last_hidden.clone(), toy.next_tok.clone()
+    toy.tok.copy_(state[0]); toy.pos.copy_(state[1]); toy.mask.copy_(state[2])
+    toy.decode_eager(dense=True)
+    dense_hidden = toy.last_hidden.clone()
+    assert _cosine(eager_hidden, dense_hidden) >= 0.999
+    toy.tok.copy_(state[0]); toy.pos.copy_(state[1]); toy.mask.copy_(state[2])
+    toy.capture()
+    assert toy.launches_per_step == 4 * toy.config.layers
+    toy.decode_graph()
+    torch.cuda.synchronize()
+    assert torch.equal(toy.last_hidden, eager_hidden) and torch.equal(toy.next_tok, eager_tok)
+    assert int(toy.pos.item()) == 25

@@ -37,6 +37,8 @@ Workspace *workspace_for(int device) {
   ws.xprep_halfs = size_t(32) * 65536;
   if (status == cudaSuccess) status = cudaMalloc(&ws.xprep, ws.xprep_halfs * sizeof(__half));
   if (status == cudaSuccess) status = cudaMalloc(&ws.xmul, 64 * sizeof(float));
+  if (status == cudaSuccess) status = cudaMalloc(&ws.status, sizeof(int));
+  if (status == cudaSuccess) status = cudaMemset(ws.status, 0, sizeof(int));
   cudaSetDevice(previous);
   if (status != cudaSuccess) {
     g_error = std::string("workspace allocation failed: ") + cudaGetErrorString(status);
@@ -279,6 +281,19 @@ int tx_kernel_info(int backend, int64_t out[9]) {
   if (backend == 0) return gemv_kernel_info(out);
   if (backend >= 5 && backend <= 9) return prefill_kernel_info(backend, out);
   return fail(TX_EINVAL, "kernel info exists for backend 0 and 5..9");
+}
+
+int tx_kernel_status(int device, int clear) {
+  Workspace *ws = workspace_for(device);
+  if (!ws) return TX_ECUDA;
+  int current = 0, value = 0;
+  TX_CUDA(cudaGetDevice(&current));
+  TX_CUDA(cudaSetDevice(device));
+  cudaError_t status = cudaMemcpy(&value, ws->status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (status == cudaSuccess && clear && value) status = cudaMemset(ws->status, 0, sizeof(int));
+  cudaSetDevice(current);
+  if (status != cudaSuccess) return fail(TX_ECUDA, std::string("tx_kernel_status: ") + cudaGetErrorString(status));
+  return value;
 }
 
 int tx_free(uint64_t handle) {

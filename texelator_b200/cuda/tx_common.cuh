@@ -62,6 +62,7 @@ struct Workspace {
   __half *xprep = nullptr;        // scaled fp16 activations of multi-token decode passes
   size_t xprep_halfs = 0;
   float *xmul = nullptr;          // per-token multipliers (64 floats)
+  int *status = nullptr;          // first non-zero code a kernel recorded when a bounded wait ran out
   int sm_count = 0;
 };
 

@@ -1,0 +1,328 @@
+"""Dense decoder harness around the BC4 linear operator.
+
+The reference drives Hugging Face models (``texelator/modeling.py:9-31`` loads them,
+``texelator/cli.py:189-219`` calls ``generate``) and replaces their seven projection
+linears per layer.  Checkpoints are not available here, so this module builds the
+same architecture family (Qwen2/Llama-style: RMSNorm, RoPE, grouped-query attention,
+SwiGLU) from a config with random-init weights, BC4-encodes the projections, and
+runs a CUDA-graphed batch-1 decode loop so that tokens/s reflects the operator and
+not Python.  q/k/v and gate/up are packed as one BC4 matrix each (rows concatenated;
+row scales are per row, so fusing changes no value).
+
+Tensor parallelism (new; the reference is single-GPU, README.md:145-148): q/k/v and
+gate/up are split by output rows, o and down by 16-column blocks with the full row
+scale vector, followed by an all-reduce over ``torch.distributed`` (NCCL).
+
+``input_device`` keeps the reference's helper (modeling.py:26-31).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import runtime
+
+
+@dataclass(frozen=True)
+class DecoderConfig:
+    name: str
+    hidden: int
+    layers: int
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    intermediate: int
+    vocab: int
+    rope_theta: float = 1e6
+    rms_eps: float = 1e-6
+    qkv_bias: bool = False
+
+    @property
+    def q_rows(self) -> int:
+        return self.q_heads * self.head_dim
+
+    @property
+    def kv_rows(self) -> int:
+        return self.kv_heads * self.head_dim
+
+    def bc4_bytes_per_token(self) -> int:
+        """BC4 blocks + fp32 row scales read per decoded token (all seven projections)."""
+        h, i = self.hidden, self.intermediate
+        shapes = [(self.q_rows, h), (self.kv_rows, h), (self.kv_rows, h), (h, self.q_rows), (i, h), (i, h), (h, i)]
+        return self.layers * sum(m * k // 2 + 4 * m for m, k in shapes)
+
+
+CONFIGS = {
+    # BASELINE.json configs[1], [3], [4] and a toy model for tests
+    "qwen2.5-3b-shaped": DecoderConfig("qwen2.5-3b-shaped", 2048, 36, 16, 2, 128, 11008, 151936, qkv_bias=True),
+    "27b-class": DecoderConfig("27b-class", 5120, 64, 40, 8, 128, 17408, 151936),
+    "70b-class": DecoderConfig("70b-class", 8192, 80, 64, 8, 128, 28672, 128256, rope_theta=5e5),
+    "toy": DecoderConfig("toy", 256, 2, 4, 2, 64, 512, 1024, qkv_bias=True),
+}
+
+
+def input_device(model) -> torch.device:
+    embedding = model.get_input_embeddings()
+    device = getattr(embedding, "output_device", embedding.weight.device)
+    if device.type == "meta":
+        raise RuntimeError("input embedding remains on a meta device")
+    return device
+
+
+# ---------------------------------------------------------------------------
+# GPU-side min/max BC4 encoder for synthetic weights (the initialisation step of
+# texelator/encoder.py:46-51 without the endpoint search; throughput inputs only).
+# ---------------------------------------------------------------------------
+
+def software_palette_table(device) -> torch.Tensor:
+    """``[255, 255, 8]`` fp32 software BC4-SNORM palette, ``lut[e1+127, e0+127, s]``."""
+    e = torch.arange(-127, 128, device=device, dtype=torch.int32)
+    e0, e1 = e[None, :, None], e[:, None, None]
+    g8 = torch.tensor([0, 7, 1, 2, 3, 4, 5, 6], device=device, dtype=torch.int32)[None, None, :]
+    g6 = torch.tensor([0, 5, 1, 2, 3, 4, 0, 0], device=device, dtype=torch.int32)[None, None, :]
+    p8 = ((7 - g8) * e0 + g8 * e1).float() / 889.0
+    p6 = ((5 - g6) * e0 + g6 * e1).float() / 635.0
+    p6[:, :, 6] = -1.0
+    p6[:, :, 7] = 1.0
+    return torch.where(e0 > e1, p8, p6).contiguous()
+
+
+@torch.no_grad()
+def encode_minmax_cuda(weight: torch.Tensor, lut: torch.Tensor, rows_per_chunk: int = 2048):
+    """BC4-encode a CUDA fp32/bf16 ``[M, K]`` matrix; returns (blocks uint8 ``[M*K/2]``, scales fp32 ``[M]``)."""
+    m, k = weight.shape
+    blocks = torch.empty((m, k // 16, 8), dtype=torch.uint8, device=weight.device)
+    scales = torch.empty(m, dtype=torch.float32, device=weight.device)
+    shifts = (3 * torch.arange(16, device=weight.device, dtype=torch.int64))[None, :]
+    for start in range(0, m, rows_per_chunk):
+        rows = weight[start:start + rows_per_chunk].float()
+        sc = rows.abs().amax(1).clamp_min(1e-12)
+        v = (rows / sc[:, None]).clamp(-1, 1).reshape(-1, 16)
+        e0 = torch.round(v.max(1).values * 127).clamp(-127, 127).long()
+        e1 = torch.round(v.min(1).values * 127).clamp(-127, 127).long()
+        pal = lut[e1 + 127, e0 + 127]                                  # [n, 8]
+        sel = (v[:, :, None] - pal[:, None, :]).abs().argmin(2)        # [n, 16]
+        word = (sel << shifts).sum(1)                                   # 48-bit selector word
+        out = blocks[start:start + rows_per_chunk].reshape(-1, 8)
+        out[:, 0] = (e0 & 255).to(torch.uint8)
+        out[:, 1] = (e1 & 255).to(torch.uint8)
+        for byte in range(6):
+            out[:, 2 + byte] = ((word >> (8 * byte)) & 255).to(torch.uint8)
+        scales[start:start + rows_per_chunk] = sc
+    return blocks.reshape(-1), scales
+
+
+def _rope_tables(config: DecoderConfig, max_len: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    half = config.head_dim // 2
+    inv = 1.0 / (config.rope_theta ** (torch.arange(0, half, device=device, dtype=torch.float32) / half))
+    ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+    return ang.cos(), ang.sin()
+
+
+def _apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x ``[T, heads, d]``; cos/sin ``[T, d/2]`` (rotate-half convention of Qwen2/Llama)."""
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half].float(), x[..., half:].float()
+    c, s = cos[:, None, :], sin[:, None, :]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+
+def _rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(x.dtype)
+
+
+class BC4Decoder:
+    """Random-init dense decoder whose projections are BC4 handles.
+
+    ``tp_world > 1`` builds this rank's shard of every projection (see module docstring) and
+    all-reduces after o/down over ``group``.  ``keep_dense`` also keeps ``bf16(pal*scale)``
+    copies of every projection (from ``ext.dequant``) so that ``forward(..., dense=True)`` runs
+    the same model through ``torch.matmul`` -- the dequantise-then-matmul comparison.
+    """
+
+    def __init__(self, config: DecoderConfig, device, max_len: int, seed: int = 0, tp_rank: int = 0,
+                 tp_world: int = 1, group=None, lookahead: int = 2, keep_dense: bool = False,
+                 weight_std: float = 0.02, prefill_backend: int = 5):
+        self.config, self.device, self.max_len = config, torch.device(device), max_len
+        self.rank, self.world, self.group = tp_rank, tp_world, group
+        self.ext = runtime.extension()
+        c = config
+        if c.q_heads % tp_world or c.kv_heads % tp_world or (c.intermediate // 16) % tp_world or (c.q_rows // 16) % tp_world:
+            raise ValueError(f"{c.name} cannot be split {tp_world}-way (heads and 16-column blocks must divide)")
+        self.q_loc, self.kv_loc, self.i_loc = c.q_rows // tp_world, c.kv_rows // tp_world, c.intermediate // tp_world
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        lut = software_palette_table(self.device)
+        self.handles: list[int] = []
+        self.h_qkv, self.h_o, self.h_gu, self.h_down = [], [], [], []
+        self.dense = [] if keep_dense else None
+        self.norm1, self.norm2 = [], []
+
+        def randn(rows, cols):
+            return torch.randn(rows, cols, device=self.device, generator=gen) * weight_std
+
+        def rows_of(mat, per):          # this rank's slice of the output rows
+            return mat[tp_rank * per:(tp_rank + 1) * per]
+
+        with torch.cuda.device(self.device):
+            for _ in range(c.layers):
+                wq, wk, wv = randn(c.q_rows, c.hidden), randn(c.kv_rows, c.hidden), randn(c.kv_rows, c.hidden)
+                wqkv = torch.cat([rows_of(wq, self.q_loc), rows_of(wk, self.kv_loc), rows_of(wv, self.kv_loc)])
+                del wq, wk, wv
+                bias = None
+                if c.qkv_bias:
+                    bias = (torch.randn(wqkv.shape[0], device=self.device, generator=gen) * 0.02).bfloat16()
+                self.h_qkv.append(self._pack_rows(wqkv, lut, bias))
+                del wqkv
+                self.h_o.append(self._pack_columns(randn(c.hidden, c.q_rows), lut))
+                wg, wu = randn(c.intermediate, c.hidden), randn(c.intermediate, c.hidden)
+                wgu = torch.cat([rows_of(wg, self.i_loc), rows_of(wu, self.i_loc)])
+                del wg, wu
+                self.h_gu.append(self._pack_rows(wgu, lut, None))
+                del wgu
+                self.h_down.append(self._pack_columns(randn(c.hidden, c.intermediate), lut))
+                self.norm1.append((1 + 0.1 * torch.randn(c.hidden, device=self.device, generator=gen)).bfloat16())
+                self.norm2.append((1 + 0.1 * torch.randn(c.hidden, device=self.device, generator=gen)).bfloat16())
+            self.final_norm = torch.ones(c.hidden, device=self.device, dtype=torch.bfloat16)
+            self.embed = (torch.randn(c.vocab, c.hidden, device=self.device, generator=gen) * 0.02).bfloat16()
+            self.lm_head = (torch.randn(c.vocab, c.hidden, device=self.device, generator=gen) * 0.02).bfloat16()
+            for h in self.handles:
+                self.ext.set_lookahead(h, lookahead)
+                self.ext.set_prefill_backend(h, prefill_backend)
+            self.cos, self.sin = _rope_tables(c, max_len, self.device)
+            kv_heads = c.kv_heads // tp_world
+            self.k_cache = torch.zeros(c.layers, kv_heads, max_len, c.head_dim, device=self.device, dtype=torch.bfloat16)
+            self.v_cache = torch.zeros_like(self.k_cache)
+            # static decode state (CUDA graph)
+            self.tok = torch.zeros(1, dtype=torch.int64, device=self.device)
+            self.pos = torch.zeros(1, dtype=torch.int64, device=self.device)
+            self.mask = torch.zeros(1, 1, 1, max_len, dtype=torch.bool, device=self.device)
+            self.next_tok = torch.zeros(1, dtype=torch.int64, device=self.device)
+            self.last_hidden = torch.zeros(1, c.hidden, dtype=torch.bfloat16, device=self.device)
+        self.graph = None
+        self.launches_per_step = 0
+
+    # -- packing ---------------------------------------------------------------
+    def _register(self, handle, bias=None):
+        self.handles.append(handle)
+        if self.dense is not None:
+            self.dense.append((handle, self.ext.dequant(handle, runtime.DEQUANT_SCALED_BF16), bias))
+        return handle
+
+    def _pack_rows(self, weight, lut, bias):
+        blocks, scales = encode_minmax_cuda(weight, lut)
+        return self._register(self.ext.pack_encoded_device(blocks, scales, bias), bias)
+
+    def _pack_columns(self, weight, lut):
+        """Row-parallel shard: encode the full matrix (row scales come from full rows), keep this
+        rank's 16-column blocks of every row."""
+        blocks, scales = encode_minmax_cuda(weight, lut)
+        if self.world > 1:
+            m, k = weight.shape
+            per = (k // 16) // self.world
+            blocks = blocks.reshape(m, k // 16, 8)[:, self.rank * per:(self.rank + 1) * per].contiguous().reshape(-1)
+        return self._register(self.ext.pack_encoded_device(blocks, scales, None))
+
+    # -- forward -----------------------------------------------------------------
+    def _linear(self, handle, x, dense):
+        if not dense:
+            return self.ext.linear(handle, x)
+        _, w, bias = next(item for item in self.dense if item[0] == handle)
+        y = (x.float() @ w.float().T)
+        return (y + bias.float() if bias is not None else y).to(x.dtype)
+
+    def _reduce(self, t):
+        if self.world > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+        return t
+
+    def _layer(self, layer, h, cos, sin, write_index, attend, dense=False):
+        c = self.config
+        tokens = h.shape[0]
+        x = _rmsnorm(h, self.norm1[layer], c.rms_eps)
+        qkv = self._linear(self.h_qkv[layer], x, dense)
+        q = qkv[:, :self.q_loc].reshape(tokens, -1, c.head_dim)
+        k = qkv[:, self.q_loc:self.q_loc + self.kv_loc].reshape(tokens, -1, c.head_dim)
+        v = qkv[:, self.q_loc + self.kv_loc:].reshape(tokens, -1, c.head_dim)
+        q, k = _apply_rope(q, cos, sin), _apply_rope(k, cos, sin)
+        self.k_cache[layer].index_copy_(1, write_index, k.transpose(0, 1))
+        self.v_cache[layer].index_copy_(1, write_index, v.transpose(0, 1))
+        out = attend(layer, q.transpose(0, 1).unsqueeze(0))                     # [1, Hq, T, d]
+        out = out.squeeze(0).transpose(0, 1).reshape(tokens, self.q_loc).contiguous()
+        h = h + self._reduce(self._linear(self.h_o[layer], out, dense))
+        x = _rmsnorm(h, self.norm2[layer], c.rms_eps)
+        gu = self._linear(self.h_gu[layer], x, dense)
+        act = (F.silu(gu[:, :self.i_loc].float()) * gu[:, self.i_loc:].float()).to(h.dtype)
+        return h + self._reduce(self._linear(self.h_down[layer], act, dense))
+
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor, dense: bool = False) -> torch.Tensor:
+        """Run a prompt from position 0, fill the KV cache, return the final hidden states ``[T, hidden]``."""
+        tokens = ids.numel()
+        index = torch.arange(tokens, device=self.device)
+        cos, sin = self.cos[:tokens], self.sin[:tokens]
+
+        def attend(layer, q):
+            k = self.k_cache[layer][:, :tokens].unsqueeze(0)
+            v = self.v_cache[layer][:, :tokens].unsqueeze(0)
+            return F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+
+        h = self.embed.index_select(0, ids.to(self.device).reshape(-1))
+        for layer in range(self.config.layers):
+            h = self._layer(layer, h, cos, sin, index, attend, dense)
+        h = _rmsnorm(h, self.final_norm, self.config.rms_eps)
+        self.pos.fill_(tokens)
+        self.mask.zero_()
+        self.mask[..., :tokens] = True
+        return h
+
+    def _decode_step(self, dense: bool = False):
+        cos, sin = self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos)
+        self.mask.index_fill_(3, self.pos, True)
+
+        def attend(layer, q):
+            return F.scaled_dot_product_attention(q, self.k_cache[layer].unsqueeze(0), self.v_cache[layer].unsqueeze(0),
+                                                  attn_mask=self.mask, enable_gqa=True)
+
+        h = self.embed.index_select(0, self.tok)
+        for layer in range(self.config.layers):
+            h = self._layer(layer, h, cos, sin, self.pos, attend, dense)
+        h = _rmsnorm(h, self.final_norm, self.config.rms_eps)
+        self.last_hidden.copy_(h)
+        logits = h @ self.lm_head.T
+        self.next_tok.copy_(logits.float().argmax(-1))
+        self.tok.copy_(self.next_tok)
+        self.pos.add_(1)
+
+    @torch.no_grad()
+    def decode_eager(self, dense: bool = False) -> None:
+        self._decode_step(dense)
+
+    @torch.no_grad()
+    def capture(self) -> None:
+        """Capture one decode step (all layers, lm_head, argmax, position update) in a CUDA graph."""
+        stream = torch.cuda.Stream(self.device)
+        saved = (self.tok.clone(), self.pos.clone(), self.mask.clone())
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                self._decode_step()
+            self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
+            stream.synchronize()
+            before = self.ext.launch_count()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=stream):
+                self._decode_step()
+            self.launches_per_step = self.ext.launch_count() - before
+            self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
+            stream.synchronize()
+        self.stream = stream
+
+    def decode_graph(self) -> None:
+        self.graph.replay()
+
+    def free(self) -> None:
+        runtime.free(self.handles)
+        self.handles = []

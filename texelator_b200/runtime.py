@@ -57,6 +57,7 @@ C_API = {
     "tx_software_palette": (_i32, [_i32, _vp]),
     "tx_dequant": (_i32, [_u64, _vp, _i32, _vp]),
     "tx_unpack_blocks": (_i32, [_u64, _vp]),
+    "tx_kernel_status": (_i32, [_i32, _i32]),
     "tx_launch_count": (ctypes.c_int64, []),
 }
 
@@ -261,6 +262,13 @@ class _Extension:
         out = torch.empty(m * k // 2, dtype=torch.uint8)
         self._check(self._lib.tx_unpack_blocks(handle, out.data_ptr()))
         return out
+
+    def kernel_status(self, clear: bool = False, device: int | None = None) -> int:
+        """0 when no kernel of this library ever gave up on a bounded wait on this device."""
+        value = self._lib.tx_kernel_status(self._device_index(device), int(clear))
+        if value < 0:
+            self._check(value)
+        return value
 
     def launch_count(self) -> int:
         return int(self._lib.tx_launch_count())
