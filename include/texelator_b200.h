@@ -12,8 +12,8 @@
  *
  * Threading: like the reference, a handle is not safe for concurrent use from several host
  * threads, and setters are plain field writes.  All launches of one process on one device share
- * a per-device split-K workspace, so tx_linear calls on the same device must be ordered on one
- * stream (or otherwise serialised) with respect to each other.
+ * a per-device activation scratch (multi-token decode), so tx_linear calls on the same device must
+ * be ordered on one stream (or otherwise serialised) with respect to each other.
  */
 #ifndef TEXELATOR_B200_H
 #define TEXELATOR_B200_H
