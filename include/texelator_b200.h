@@ -73,6 +73,16 @@ int tx_pack_encoded_shard(const uint8_t *blocks, size_t nbytes, const float *sca
  * allocates with at::empty); both of `dtype`.  Asynchronous on `stream`. */
 int tx_linear(uint64_t handle, const void *x, void *y, int tokens, int dtype, void *stream);
 
+/* No counterpart in the reference.  Same result as tx_linear for a small token group (1..32 tokens,
+ * tokens * K <= 262144 with K rounded up to 128, one shared-memory pass), but the fp16 activation
+ * scratch of the multi-token decode kernel is a fixed array inside the library image instead of
+ * memory from cudaMalloc, and the call allocates nothing on the device.  Meant for hosts that cannot
+ * allocate when they need the linear (all memory owned by their own pool, a stream being captured, a
+ * thread that must not take the allocator lock).  Larger requests fail with TX_EINVAL.  The first
+ * call on a device looks the array's address up (cudaGetSymbolAddress); make that call before any
+ * stream capture.  Every call on a device uses the same array: calls that overlap on the GPU race. */
+int tx_linear_static_scratch(uint64_t handle, const void *x, void *y, int tokens, int dtype, void *stream);
+
 /* set_lookahead: texelator_cuda.cu:1471-1478.  k in {1,2,3,4,6,8}: 1 KiB weight requests each
  * warp keeps in flight (the reference: texture requests in flight). */
 int tx_set_lookahead(uint64_t handle, int lookahead);

@@ -194,6 +194,21 @@ int tx_linear(uint64_t handle, const void *x, void *y, int tokens, int dtype, vo
   return rc;
 }
 
+int tx_linear_static_scratch(uint64_t handle, const void *x, void *y, int tokens, int dtype, void *stream_ptr) {
+  Handle *h = as_handle(handle);
+  if (!h) return fail(TX_EINVAL, "null Texelator handle");
+  if (!x || !y || dtype != TX_DTYPE_BF16) return fail(TX_EINVAL, "input must be contiguous CUDA BF16");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15)
+    return fail(TX_EINVAL, "activation and output pointers must be 16-byte aligned");
+  int current = 0;
+  TX_CUDA(cudaGetDevice(&current));
+  if (current != h->device) TX_CUDA(cudaSetDevice(h->device));
+  int rc = launch_gemv_static_scratch(h, static_cast<const __nv_bfloat16 *>(x), static_cast<__nv_bfloat16 *>(y), tokens,
+                                      static_cast<cudaStream_t>(stream_ptr));
+  if (current != h->device) cudaSetDevice(current);
+  return rc;
+}
+
 int tx_set_lookahead(uint64_t handle, int lookahead) {
   Handle *h = as_handle(handle);
   if (!h) return fail(TX_EINVAL, "null Texelator handle");

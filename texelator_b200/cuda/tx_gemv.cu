@@ -509,6 +509,92 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
   return TX_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// Multi-token decode without any allocation.
+//
+// Some hosts may not allocate device memory at the moment they need a linear: a serving loop that
+// has handed all memory to its own pool, code running between cudaStreamBeginCapture/EndCapture,
+// or a real-time thread that must not take the allocator lock.  For them the rescaled fp16
+// activations of the multi-token decode pass live in a fixed array that is part of the library
+// image instead of the per-device workspace that tx_pack_encoded allocates.  Every GPU that loads
+// the library carries the array (about 0.5 MiB) until the process exits.
+//
+// Limits: tokens <= 32 and tokens * K (K rounded up to 128) <= kStaticActivationHalfs, and the
+// token group must fit one shared-memory pass.  The pre-pass rewrites every element the main kernel
+// reads (including the zero padding), so nothing depends on what an earlier call left behind; but
+// all calls on a device share the one array, so two calls that overlap on the GPU race.
+// ------------------------------------------------------------------------------------------
+constexpr size_t kStaticActivationHalfs = size_t(8) * 32768;
+static __device__ __align__(256) __half g_static_activations[kStaticActivationHalfs];
+static __device__ __align__(256) float g_static_multipliers[64];
+
+struct StaticScratch {
+  __half *activations = nullptr;   // device addresses of the two arrays on one device
+  float *multipliers = nullptr;
+  int sm_count = 0;
+  bool ready = false;
+};
+
+// The array names above are host-side stand-ins; the device addresses come from
+// cudaGetSymbolAddress, once per device, with that device current.
+static int static_scratch_for(int device, StaticScratch **out) {
+  static StaticScratch table[64];
+  static std::mutex guard;
+  if (device < 0 || device >= 64) return fail(TX_EINVAL, "device index outside 0..63");
+  std::lock_guard<std::mutex> lock(guard);
+  StaticScratch &entry = table[device];
+  if (!entry.ready) {
+    TX_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&entry.activations), g_static_activations));
+    TX_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&entry.multipliers), g_static_multipliers));
+    TX_CUDA(cudaDeviceGetAttribute(&entry.sm_count, cudaDevAttrMultiProcessorCount, device));
+    entry.ready = true;
+  }
+  *out = &entry;
+  return TX_OK;
+}
+
+int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream) {
+  const int KP = h->KI * 128;
+  if (tokens < 1 || tokens > 8 * kMaxTokenTiles)
+    return fail(TX_EINVAL, "tx_linear_static_scratch handles 1..32 tokens per call");
+  if (size_t(tokens) * KP > kStaticActivationHalfs)
+    return fail(TX_EINVAL, "tokens * K exceeds the built-in activation scratch (262144 fp16 values); use tx_linear");
+  const int nt = token_tiles(tokens);
+  const size_t smem = gemv_smem_bytes(KP, tokens, nt);
+  if (smem > kSmemBudget)
+    return fail(TX_EINVAL, "this many tokens of this K do not fit one shared-memory pass; use tx_linear");
+  StaticScratch *scratch = nullptr;
+  int rc = static_scratch_for(h->device, &scratch);
+  if (rc != TX_OK) return rc;
+  GemvKernel kernel = pick_kernel(h->lookahead, nt, true);
+  TX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
+  int per_sm = 0;
+  TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem));
+  if (per_sm < 1) return fail(TX_EINVAL, "decode GEMV does not fit in shared memory for this K");
+  GemvParams p{};
+  p.tiles = reinterpret_cast<const uint4 *>(h->tiles);
+  p.flags = h->unit_flags;
+  p.scales = h->scales;
+  p.bias = h->bias;
+  p.x = x;
+  p.y = y;
+  p.M = h->M;
+  p.K = h->K;
+  p.KI = h->KI;
+  p.MT = h->MT;
+  p.T = tokens;
+  p.KP = KP;
+  p.xprep = scratch->activations;
+  p.xmul = scratch->multipliers;
+  gemv_xprep_kernel<<<tokens, kGemvThreads, 0, stream>>>(x, scratch->activations, scratch->multipliers, h->K, KP);
+  count_launch();
+  const int grid = std::max(1, std::min(h->MT, scratch->sm_count * std::min(per_sm, 3)));
+  kernel<<<grid, kGemvThreads, smem, stream>>>(p);
+  count_launch();
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
 int gemv_kernel_info(int64_t out[9]) {
   cudaFuncAttributes attributes{};
   GemvKernel kernel = gemv_tile_kernel<2, 1, false>;

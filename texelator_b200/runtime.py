@@ -46,6 +46,7 @@ C_API = {
     "tx_pack_encoded_shard": (_i32, [_vp, _sz, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32,
                                      ctypes.POINTER(_u64)]),
     "tx_linear": (_i32, [_u64, _vp, _vp, _i32, _i32, _vp]),
+    "tx_linear_static_scratch": (_i32, [_u64, _vp, _vp, _i32, _i32, _vp]),
     "tx_set_lookahead": (_i32, [_u64, _i32]),
     "tx_set_prefill": (_i32, [_u64, _i32, _i32]),
     "tx_set_prefill_backend": (_i32, [_u64, _i32]),
@@ -182,6 +183,19 @@ class _Extension:
             raise RuntimeError("input shape/device mismatch")
         stream = torch.cuda.current_stream(device).cuda_stream
         self._check(self._lib.tx_linear(handle, x.data_ptr(), y.data_ptr(), tokens, DTYPE_BF16, stream))
+        return y
+
+    def linear_static_scratch(self, handle: int, x: torch.Tensor) -> torch.Tensor:
+        """``linear`` for a small token group through the entry point that allocates nothing on the
+        device: its activation scratch is a fixed array inside the library (for callers whose memory
+        is all in their own pool, or who are between capture begin/end).  Raises for requests beyond
+        32 tokens or 262144 activation values.  Calls on one device must not overlap on the GPU."""
+        m, k, device = self._shapes[handle]
+        if not x.is_cuda or x.dtype != torch.bfloat16 or not x.is_contiguous() or x.size(-1) != k:
+            raise RuntimeError("input must be contiguous CUDA BF16 [..., K]")
+        y = torch.empty(x.shape[:-1] + (m,), dtype=x.dtype, device=x.device)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        self._check(self._lib.tx_linear_static_scratch(handle, x.data_ptr(), y.data_ptr(), x.numel() // k, DTYPE_BF16, stream))
         return y
 
     def set_lookahead(self, handle: int, lookahead: int) -> None:
