@@ -112,6 +112,7 @@ def cpu_baseline_sample(config, seconds: float = 10.0) -> dict:
     about ``seconds`` on this host, and extrapolate linearly (bytes) to one decoded token."""
     from oracle import bc4_oracle as O
     k = config.hidden
+    torch.set_num_threads(max(torch.get_num_threads(), os.cpu_count() or 1))   # torchrun pins OMP_NUM_THREADS=1
     if "lut" not in _CPU_CACHE:
         lut_np = O.software_palette()
         rng = np.random.default_rng(0)
@@ -191,11 +192,13 @@ def timed_steps(model, steps: int, warmup: int, world: int, e2e: bool) -> float:
             dist.barrier()
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.cudart().cudaProfilerStart()      # lets `ncu --profile-from-start off` see only the timed steps
         begin.record(stream)
         for _ in range(steps):
             one()
         end.record(stream)
         stream.synchronize()
+        torch.cuda.cudart().cudaProfilerStop()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -294,9 +297,16 @@ def run_gpu_arm(args, config) -> None:
             "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
-    model.free()
+    sys.stdout.flush()
+    # Tear down in an order that cannot block: graphs that captured NCCL kernels go first, every rank
+    # meets at a barrier, and multi-rank runs leave without destroying the communicator (its destructor
+    # can wait for ever on captured work).
+    model.graph = None
     if world > 1:
-        dist.destroy_process_group()
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
+    model.free()
 
 
 def main() -> None:

@@ -77,8 +77,8 @@ int tx_linear(uint64_t handle, const void *x, void *y, int tokens, int dtype, vo
  * tokens * K <= 262144 with K rounded up to 128, one shared-memory pass), but the fp16 activation
  * scratch of the multi-token decode kernel is a fixed array inside the library image instead of
  * memory from cudaMalloc, and the call allocates nothing on the device.  Meant for hosts that cannot
- * allocate when they need the linear (all memory owned by their own pool, a stream being captured, a
- * thread that must not take the allocator lock).  Larger requests fail with TX_EINVAL.  The first
+ * allocate when they need the linear (all memory owned by their own pool, a thread that must
+ * not take the allocator lock).  Larger requests fail with TX_EINVAL.  The first
  * call on a device looks the array's address up (cudaGetSymbolAddress); make that call before any
  * stream capture.  Every call on a device uses the same array: calls that overlap on the GPU race. */
 int tx_linear_static_scratch(uint64_t handle, const void *x, void *y, int tokens, int dtype, void *stream);
@@ -129,6 +129,22 @@ int tx_unpack_blocks(uint64_t handle, uint8_t *out_host);
  * accumulator wait) here and returns early.  Synchronises the device; returns the code (0 = healthy)
  * or a negative TX_E* value; `clear` resets it. */
 int tx_kernel_status(int device, int clear);
+
+/* Decode-loop glue around the linears (no counterpart in the reference, which leaves these steps to
+ * Hugging Face / PyTorch: texelator/cli.py:189-219).  All tensors bf16 on the device, fp32 arithmetic,
+ * asynchronous on `stream`.
+ *   add_rmsnorm      : h += delta (delta may be null); y = rmsnorm(h) * weight, per token row
+ *   rope_append      : rotate q and k of one token in place (rotate-half), append k and v to the
+ *                      caches [kv_heads, max_len, head_dim] at *position (device int64)
+ *   attention_decode : one query per head over cache positions 0..*position, grouped-query; `scratch`
+ *                      holds q_heads * ceil(max_len/256) * (head_dim+2) floats; head_dim must be 128
+ *   silu_mul         : out[t,i] = silu(gate_up[t,i]) * gate_up[t,intermediate+i]                     */
+int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, int tokens, int hidden, float eps, void *stream);
+int tx_aux_rope_append(void *qkv, const float *cos_table, const float *sin_table, const void *position, void *k_cache,
+                       void *v_cache, int q_heads, int kv_heads, int head_dim, int max_len, void *stream);
+int tx_aux_attention_decode(const void *qkv, const void *k_cache, const void *v_cache, const void *position, float *scratch,
+                            void *out, int q_heads, int kv_heads, int head_dim, int max_len, float scale, void *stream);
+int tx_aux_silu_mul(const void *gate_up, void *out, int tokens, int intermediate, void *stream);
 
 /* Number of this library's kernels launched by the calling process since load (all threads). */
 int64_t tx_launch_count(void);

@@ -47,3 +47,35 @@ def test_decode_graph_matches_eager_and_dense(toy):
     torch.cuda.synchronize()
     assert torch.equal(toy.last_hidden, eager_hidden) and torch.equal(toy.next_tok, eager_tok)
     assert int(toy.pos.item()) == 25
+
+
+def test_fused_decode_step_matches_pytorch_glue():
+    """The library's glue kernels (norm, RoPE + cache append, attention, SwiGLU) against the PyTorch
+    formulation of the same step, on a model with 128-wide heads."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from texelator_b200.modeling import CONFIGS, BC4Decoder
+    model = BC4Decoder(CONFIGS["toy128"], "cuda:0", max_len=600, seed=5)
+    try:
+        assert model.fused
+        ids = torch.randint(0, model.config.vocab, (300,), generator=torch.Generator().manual_seed(2))
+        model.prefill(ids)
+        model.tok.fill_(int(ids[-1]))
+        state = (model.tok.clone(), model.pos.clone(), model.mask.clone(), model.k_cache.clone(), model.v_cache.clone())
+        hidden, tokens = [], []
+        for _ in range(3):
+            model.decode_eager()
+            hidden.append(model.last_hidden.clone()); tokens.append(int(model.next_tok))
+        model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
+        model.k_cache.copy_(state[3]); model.v_cache.copy_(state[4])
+        for step in range(3):
+            model.decode_eager(fused=True)
+            assert _cosine(model.last_hidden, hidden[step]) >= 0.9995, step
+        model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
+        model.capture()
+        assert model.launches_per_step == model.config.layers * 10 + 1
+        model.decode_graph()
+        torch.cuda.synchronize()
+        assert _cosine(model.last_hidden, hidden[0]) >= 0.9995
+    finally:
+        model.free()

@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 def test_static_scratch_linear_matches_regular_linear(lut):
     """Hosts that cannot call cudaMalloc when they need the linear (memory owned by their own pool,
-    a stream being captured) use ``tx_linear_static_scratch``; it must give what ``tx_linear`` gives.
+    a thread that must not take the allocator lock) use ``tx_linear_static_scratch``; it must give what ``tx_linear`` gives.
     Two different calls in a row also show that nothing depends on what the shared array held."""
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")

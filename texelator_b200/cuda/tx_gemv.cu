@@ -140,6 +140,7 @@ gemv_tile_kernel(const GemvParams p) {
 
   // -- first loads, issued before anything else.  Prefetch addresses past the last tile fall back
   //    to the first unit (valid memory, never consumed).
+  const int tile_stride = gridDim.x;
   int ptile = blockIdx.x, pk = warp;
   uint4 pend[LOOKAHEAD][2];
   unsigned pflag[LOOKAHEAD];
@@ -153,7 +154,7 @@ gemv_tile_kernel(const GemvParams p) {
     pk += WS;
     if (pk >= KI) {
       pk = warp;
-      ptile += gridDim.x;
+      ptile += tile_stride;
     }
   };
 #pragma unroll
@@ -239,7 +240,6 @@ gemv_tile_kernel(const GemvParams p) {
     for (int slot = 0; slot < LOOKAHEAD; ++slot) {
       const uint4 q = pend[slot][0], r = pend[slot][1];
       const unsigned flag = pflag[slot];
-      prefetch(slot);
       // ---- one unit: blocks (ki*8 + t) [sub 0] and (ki*8 + 4 + t) [sub 1] of rows g and g+8
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
@@ -263,6 +263,7 @@ gemv_tile_kernel(const GemvParams p) {
           mma_f16(acc2[nt], aq[6], ar[6], aq[7], ar[7], b1.z, b1.w);
         }
       }
+      prefetch(slot);   // refill the slot only now: its registers are free, so no copies are needed
       ki += WS;
       xoff += xoff_step;
       if (ki >= KI) {
@@ -291,7 +292,7 @@ gemv_tile_kernel(const GemvParams p) {
           }
         }
         buf ^= 1;
-        tile += gridDim.x;
+        tile += tile_stride;
         if (tile >= MT) return;
         ki = warp;
         xoff = unsigned(warp) * 256;
@@ -513,8 +514,7 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
 // Multi-token decode without any allocation.
 //
 // Some hosts may not allocate device memory at the moment they need a linear: a serving loop that
-// has handed all memory to its own pool, code running between cudaStreamBeginCapture/EndCapture,
-// or a real-time thread that must not take the allocator lock.  For them the rescaled fp16
+// has handed all memory to its own pool, or a real-time thread that must not take the allocator lock.  For them the rescaled fp16
 // activations of the multi-token decode pass live in a fixed array that is part of the library
 // image instead of the per-device workspace that tx_pack_encoded allocates.  Every GPU that loads
 // the library carries the array (about 0.5 MiB) until the process exits.

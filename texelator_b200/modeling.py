@@ -61,6 +61,7 @@ CONFIGS = {
     "27b-class": DecoderConfig("27b-class", 5120, 64, 40, 8, 128, 17408, 151936),
     "70b-class": DecoderConfig("70b-class", 8192, 80, 64, 8, 128, 28672, 128256, rope_theta=5e5),
     "toy": DecoderConfig("toy", 256, 2, 4, 2, 64, 512, 1024, qkv_bias=True),
+    "toy128": DecoderConfig("toy128", 512, 3, 8, 2, 128, 1024, 2048, qkv_bias=True),
 }
 
 
@@ -202,6 +203,20 @@ class BC4Decoder:
             self.mask = torch.zeros(1, 1, 1, max_len, dtype=torch.bool, device=self.device)
             self.next_tok = torch.zeros(1, dtype=torch.int64, device=self.device)
             self.last_hidden = torch.zeros(1, c.hidden, dtype=torch.bfloat16, device=self.device)
+            # static buffers of the fused decode step
+            q_heads = c.q_heads // tp_world
+            bf = dict(dtype=torch.bfloat16, device=self.device)
+            self.buf_h = torch.zeros(1, c.hidden, **bf)
+            self.buf_x = torch.zeros(1, c.hidden, **bf)
+            self.buf_qkv = torch.zeros(1, self.q_loc + 2 * self.kv_loc, **bf)
+            self.buf_attn = torch.zeros(1, self.q_loc, **bf)
+            self.buf_o = torch.zeros(1, c.hidden, **bf)
+            self.buf_gu = torch.zeros(1, 2 * self.i_loc, **bf)
+            self.buf_act = torch.zeros(1, self.i_loc, **bf)
+            self.buf_down = torch.zeros(1, c.hidden, **bf)
+            self.attn_scratch = torch.zeros(q_heads * ((max_len + 255) // 256) * (c.head_dim + 2), dtype=torch.float32,
+                                            device=self.device)
+            self.fused = c.head_dim == 128 and (c.q_heads // c.kv_heads) <= 8
         self.graph = None
         self.launches_per_step = 0
 
@@ -297,24 +312,58 @@ class BC4Decoder:
         self.tok.copy_(self.next_tok)
         self.pos.add_(1)
 
-    @torch.no_grad()
-    def decode_eager(self, dense: bool = False) -> None:
-        self._decode_step(dense)
+    def _decode_step_fused(self):
+        """One decode step with the library's glue kernels: per layer 4 BC4 GEMVs + 6 small launches."""
+        c, ext = self.config, self.ext
+        q_heads, kv_heads = c.q_heads // self.world, c.kv_heads // self.world
+        torch.index_select(self.embed, 0, self.tok, out=self.buf_h)
+        delta = None
+        for layer in range(c.layers):
+            ext.add_rmsnorm(self.buf_h, delta, self.norm1[layer], self.buf_x, c.rms_eps)
+            ext.linear_out(self.h_qkv[layer], self.buf_x, self.buf_qkv)
+            ext.rope_append(self.buf_qkv, self.cos, self.sin, self.pos, self.k_cache[layer], self.v_cache[layer],
+                            q_heads, kv_heads, c.head_dim)
+            ext.attention_decode(self.buf_qkv, self.k_cache[layer], self.v_cache[layer], self.pos, self.attn_scratch,
+                                 self.buf_attn, q_heads, kv_heads, c.head_dim)
+            ext.linear_out(self.h_o[layer], self.buf_attn, self.buf_o)
+            self._reduce(self.buf_o)
+            ext.add_rmsnorm(self.buf_h, self.buf_o, self.norm2[layer], self.buf_x, c.rms_eps)
+            ext.linear_out(self.h_gu[layer], self.buf_x, self.buf_gu)
+            ext.silu_mul(self.buf_gu, self.buf_act)
+            ext.linear_out(self.h_down[layer], self.buf_act, self.buf_down)
+            self._reduce(self.buf_down)
+            delta = self.buf_down
+        ext.add_rmsnorm(self.buf_h, delta, self.final_norm, self.buf_x, c.rms_eps)
+        self.last_hidden.copy_(self.buf_x)
+        logits = self.buf_x @ self.lm_head.T
+        self.next_tok.copy_(logits.float().argmax(-1))
+        self.tok.copy_(self.next_tok)
+        self.mask.index_fill_(3, self.pos, True)
+        self.pos.add_(1)
 
     @torch.no_grad()
-    def capture(self) -> None:
-        """Capture one decode step (all layers, lm_head, argmax, position update) in a CUDA graph."""
+    def decode_eager(self, dense: bool = False, fused: bool = False) -> None:
+        if fused:
+            self._decode_step_fused()
+        else:
+            self._decode_step(dense)
+
+    @torch.no_grad()
+    def capture(self, fused: bool | None = None) -> None:
+        """Capture one decode step (all layers, lm_head, argmax, position update) in a CUDA graph.
+        ``fused`` (default: when the shapes allow) uses the library's glue kernels instead of PyTorch ops."""
+        step = self._decode_step_fused if (self.fused if fused is None else fused) else self._decode_step
         stream = torch.cuda.Stream(self.device)
         saved = (self.tok.clone(), self.pos.clone(), self.mask.clone())
         with torch.cuda.stream(stream):
             for _ in range(2):
-                self._decode_step()
+                step()
             self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
             stream.synchronize()
             before = self.ext.launch_count()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=stream):
-                self._decode_step()
+                step()
             self.launches_per_step = self.ext.launch_count() - before
             self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
             stream.synchronize()

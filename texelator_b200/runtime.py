@@ -59,6 +59,10 @@ C_API = {
     "tx_dequant": (_i32, [_u64, _vp, _i32, _vp]),
     "tx_unpack_blocks": (_i32, [_u64, _vp]),
     "tx_kernel_status": (_i32, [_i32, _i32]),
+    "tx_aux_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, ctypes.c_float, _vp]),
+    "tx_aux_rope_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "tx_aux_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp]),
+    "tx_aux_silu_mul": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "tx_launch_count": (ctypes.c_int64, []),
 }
 
@@ -188,7 +192,7 @@ class _Extension:
     def linear_static_scratch(self, handle: int, x: torch.Tensor) -> torch.Tensor:
         """``linear`` for a small token group through the entry point that allocates nothing on the
         device: its activation scratch is a fixed array inside the library (for callers whose memory
-        is all in their own pool, or who are between capture begin/end).  Raises for requests beyond
+        is all in their own pool, or who must not take the allocator lock).  Raises for requests beyond
         32 tokens or 262144 activation values.  Calls on one device must not overlap on the GPU."""
         m, k, device = self._shapes[handle]
         if not x.is_cuda or x.dtype != torch.bfloat16 or not x.is_contiguous() or x.size(-1) != k:
@@ -276,6 +280,30 @@ class _Extension:
         out = torch.empty(m * k // 2, dtype=torch.uint8)
         self._check(self._lib.tx_unpack_blocks(handle, out.data_ptr()))
         return out
+
+    # -- decode-loop glue kernels (see include/texelator_b200.h) ----------------
+    @staticmethod
+    def _stream(tensor: torch.Tensor) -> int:
+        return torch.cuda.current_stream(tensor.device).cuda_stream
+
+    def add_rmsnorm(self, h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, y: torch.Tensor, eps: float) -> None:
+        tokens, hidden = h.shape
+        self._check(self._lib.tx_aux_add_rmsnorm(h.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                                 weight.data_ptr(), y.data_ptr(), tokens, hidden, eps, self._stream(h)))
+
+    def rope_append(self, qkv, cos, sin, position, k_cache, v_cache, q_heads: int, kv_heads: int, head_dim: int) -> None:
+        self._check(self._lib.tx_aux_rope_append(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), position.data_ptr(),
+                                                 k_cache.data_ptr(), v_cache.data_ptr(), q_heads, kv_heads, head_dim,
+                                                 k_cache.shape[1], self._stream(qkv)))
+
+    def attention_decode(self, qkv, k_cache, v_cache, position, scratch, out, q_heads: int, kv_heads: int, head_dim: int) -> None:
+        self._check(self._lib.tx_aux_attention_decode(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), position.data_ptr(),
+                                                      scratch.data_ptr(), out.data_ptr(), q_heads, kv_heads, head_dim,
+                                                      k_cache.shape[1], float(head_dim) ** -0.5, self._stream(qkv)))
+
+    def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+        tokens, two_i = gate_up.shape
+        self._check(self._lib.tx_aux_silu_mul(gate_up.data_ptr(), out.data_ptr(), tokens, two_i // 2, self._stream(gate_up)))
 
     def kernel_status(self, clear: bool = False, device: int | None = None) -> int:
         """0 when no kernel of this library ever gave up on a bounded wait on this device."""
