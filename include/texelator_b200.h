@@ -137,7 +137,7 @@ int tx_kernel_status(int device, int clear);
  *   rope_append      : rotate q and k of one token in place (rotate-half), append k and v to the
  *                      caches [kv_heads, max_len, head_dim] at *position (device int64)
  *   attention_decode : one query per head over cache positions 0..*position, grouped-query; `scratch`
- *                      holds q_heads * ceil(max_len/256) * (head_dim+2) floats; head_dim must be 128
+ *                      holds q_heads * ceil(max_len/128) * (head_dim+2) floats; head_dim must be 128
  *   silu_mul         : out[t,i] = silu(gate_up[t,i]) * gate_up[t,intermediate+i]                     */
 int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, int tokens, int hidden, float eps, void *stream);
 int tx_aux_rope_append(void *qkv, const float *cos_table, const float *sin_table, const void *position, void *k_cache,

@@ -17,36 +17,66 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // h += delta (optional, rounded to bf16 like a PyTorch residual add); y = rmsnorm(h) * weight.
-// One CTA per token row.
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16 *__restrict__ h, const __nv_bfloat16 *__restrict__ delta,
-                                                          const __nv_bfloat16 *__restrict__ weight, __nv_bfloat16 *__restrict__ y,
-                                                          int hidden, float eps) {
-  __shared__ float partial[8];
-  const int row = blockIdx.x;
-  __nv_bfloat16 *hr = h + size_t(row) * hidden;
-  const __nv_bfloat16 *dr = delta ? delta + size_t(row) * hidden : nullptr;
+// One CTA per token row; every thread keeps its 8-element chunks in registers between the two passes.
+constexpr int kNormThreads = 512;
+constexpr int kNormChunks = 4;            // hidden <= 512 * 8 * 4 = 16384 stays in registers
+
+__global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16 *__restrict__ h, const __nv_bfloat16 *__restrict__ delta,
+                                                                   const __nv_bfloat16 *__restrict__ weight, __nv_bfloat16 *__restrict__ y,
+                                                                   int hidden, float eps) {
+  __shared__ float partial[kNormThreads / 32];
+  const int row = blockIdx.x, chunks = hidden / 8;
+  uint4 *hr = reinterpret_cast<uint4 *>(h + size_t(row) * hidden);
+  const uint4 *dr = delta ? reinterpret_cast<const uint4 *>(delta + size_t(row) * hidden) : nullptr;
+  uint4 keep[kNormChunks];
   float ss = 0.f;
-  for (int i = threadIdx.x * 2; i < hidden; i += 512) {
-    float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(hr + i));
-    if (dr) {
-      float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(dr + i));
-      __nv_bfloat162 s = __floats2bfloat162_rn(v.x + d.x, v.y + d.y);
-      *reinterpret_cast<__nv_bfloat162 *>(hr + i) = s;
-      v = __bfloat1622float2(s);
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    if (i < chunks) {
+      uint4 v = hr[i];
+      __nv_bfloat162 *pv = reinterpret_cast<__nv_bfloat162 *>(&v);
+      if (dr) {
+        uint4 d = dr[i];
+        const __nv_bfloat162 *pd = reinterpret_cast<const __nv_bfloat162 *>(&d);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float2 a = __bfloat1622float2(pv[e]), b = __bfloat1622float2(pd[e]);
+          pv[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+        }
+        hr[i] = v;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 a = __bfloat1622float2(pv[e]);
+        ss += a.x * a.x + a.y * a.y;
+      }
+      keep[c] = v;
     }
-    ss += v.x * v.x + v.y * v.y;
   }
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
   __syncthreads();
   float total = 0.f;
 #pragma unroll
-  for (int w = 0; w < 8; ++w) total += partial[w];
+  for (int w = 0; w < kNormThreads / 32; ++w) total += partial[w];
   const float inv = rsqrtf(total / float(hidden) + eps);
-  for (int i = threadIdx.x * 2; i < hidden; i += 512) {
-    float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(hr + i));
-    float2 w = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(weight + i));
-    *reinterpret_cast<__nv_bfloat162 *>(y + size_t(row) * hidden + i) = __floats2bfloat162_rn(v.x * inv * w.x, v.y * inv * w.y);
+  const uint4 *wr = reinterpret_cast<const uint4 *>(weight);
+  uint4 *yr = reinterpret_cast<uint4 *>(y + size_t(row) * hidden);
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    if (i < chunks) {
+      uint4 v = keep[c], w = wr[i], o;
+      const __nv_bfloat162 *pv = reinterpret_cast<const __nv_bfloat162 *>(&v), *pw = reinterpret_cast<const __nv_bfloat162 *>(&w);
+      __nv_bfloat162 *po = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 a = __bfloat1622float2(pv[e]), g = __bfloat1622float2(pw[e]);
+        po[e] = __floats2bfloat162_rn(a.x * inv * g.x, a.y * inv * g.y);
+      }
+      yr[i] = o;
+    }
   }
 }
 
@@ -83,99 +113,97 @@ __global__ void __launch_bounds__(64) rope_append_kernel(__nv_bfloat16 *__restri
 }
 
 // Single-query attention over cache positions [0, pos], split along the sequence: CTA (split, kv head)
-// scores kKeys keys for the G query heads of its group, then accumulates p*V with one thread per
-// head dimension.  Unnormalised partial outputs and (max, sum) go to `partial`.
-constexpr int kKeys = 256;
+// handles kKeys keys for the G query heads of its group.  Scores: one warp per key, lanes across the
+// head dimension (coalesced 256-byte key rows, q in registers).  Values: one thread per head dimension
+// and key parity.  Unnormalised partial outputs and (max, sum) go to `partial`.
+constexpr int kKeys = 128;
 constexpr int kMaxGroup = 8;
 constexpr int kHeadDim = 128;
+constexpr int kAttnThreads = 256;
 
-__global__ void __launch_bounds__(kHeadDim) attention_partial_kernel(const __nv_bfloat16 *__restrict__ qkv,
-                                                                     const __nv_bfloat16 *__restrict__ k_cache,
-                                                                     const __nv_bfloat16 *__restrict__ v_cache,
-                                                                     const long long *__restrict__ position, float *__restrict__ partial,
-                                                                     int q_heads, int kv_heads, int max_len, float scale) {
-  __shared__ float q_s[kMaxGroup][kHeadDim];
+__global__ void __launch_bounds__(kAttnThreads) attention_partial_kernel(const __nv_bfloat16 *__restrict__ qkv,
+                                                                         const __nv_bfloat16 *__restrict__ k_cache,
+                                                                         const __nv_bfloat16 *__restrict__ v_cache,
+                                                                         const long long *__restrict__ position, float *__restrict__ partial,
+                                                                         int q_heads, int kv_heads, int max_len, float scale) {
   __shared__ float p_s[kMaxGroup][kKeys];
-  __shared__ float red[kMaxGroup][4];
+  __shared__ float acc_s[kMaxGroup][kHeadDim];
   const int split = blockIdx.x, kvh = blockIdx.y, splits = gridDim.x;
   const int group = q_heads / kv_heads;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const long long last = *position;                       // attends to keys 0..last
   const int key0 = split * kKeys;
-  const int count = int(min((long long)kKeys, last + 1 - key0));   // may be <= 0
-  for (int g = 0; g < group; ++g) q_s[g][tid] = __bfloat162float(qkv[size_t(kvh * group + g) * kHeadDim + tid]) * scale;
-  __syncthreads();
-  float local_max[kMaxGroup];
+  const int count = int(max(0ll, min((long long)kKeys, last + 1 - key0)));
+  // q: lane owns dimensions 4*lane .. 4*lane+3 of every query head of the group
+  float q[kMaxGroup][4];
 #pragma unroll
-  for (int g = 0; g < kMaxGroup; ++g) local_max[g] = -INFINITY;
-  for (int j = tid; j < kKeys; j += kHeadDim) {
+  for (int g = 0; g < kMaxGroup; ++g) {
+    if (g < group) {
+      uint2 raw = *reinterpret_cast<const uint2 *>(qkv + size_t(kvh * group + g) * kHeadDim + 4 * lane);
+      float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&raw.y));
+      q[g][0] = a.x * scale; q[g][1] = a.y * scale; q[g][2] = b.x * scale; q[g][3] = b.y * scale;
+    } else {
+      q[g][0] = q[g][1] = q[g][2] = q[g][3] = 0.f;
+    }
+  }
+  for (int j = warp; j < kKeys; j += kAttnThreads / 32) {
     float dot[kMaxGroup];
 #pragma unroll
     for (int g = 0; g < kMaxGroup; ++g) dot[g] = 0.f;
     if (j < count) {
-      const uint4 *row = reinterpret_cast<const uint4 *>(k_cache + (size_t(kvh) * max_len + key0 + j) * kHeadDim);
-#pragma unroll 4
-      for (int c = 0; c < kHeadDim / 8; ++c) {
-        uint4 raw = row[c];
-        const __nv_bfloat162 *pairs = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+      uint2 raw = *reinterpret_cast<const uint2 *>(k_cache + (size_t(kvh) * max_len + key0 + j) * kHeadDim + 4 * lane);
+      float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&raw.y));
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float2 kv = __bfloat1622float2(pairs[e]);
-#pragma unroll
-          for (int g = 0; g < kMaxGroup; ++g)
-            if (g < group) dot[g] += kv.x * q_s[g][c * 8 + 2 * e] + kv.y * q_s[g][c * 8 + 2 * e + 1];
-        }
-      }
+      for (int g = 0; g < kMaxGroup; ++g)
+        if (g < group) dot[g] = a.x * q[g][0] + a.y * q[g][1] + b.x * q[g][2] + b.y * q[g][3];
     }
 #pragma unroll
     for (int g = 0; g < kMaxGroup; ++g)
       if (g < group) {
-        float s = j < count ? dot[g] : -INFINITY;
-        p_s[g][j] = s;
-        local_max[g] = fmaxf(local_max[g], s);
+        float s = warp_sum(dot[g]);
+        if (lane == 0) p_s[g][j] = j < count ? s : -INFINITY;
       }
   }
-  for (int g = 0; g < group; ++g) {
-    float m = warp_max(local_max[g]);
-    if (lane == 0) red[g][warp] = m;
-  }
   __syncthreads();
-  float gmax[kMaxGroup], gsum[kMaxGroup];
-#pragma unroll
-  for (int g = 0; g < kMaxGroup; ++g) {
-    gmax[g] = g < group ? fmaxf(fmaxf(red[g][0], red[g][1]), fmaxf(red[g][2], red[g][3])) : 0.f;
-    gsum[g] = 0.f;
-  }
-  __syncthreads();
-  for (int j = tid; j < kKeys; j += kHeadDim)
-    for (int g = 0; g < group; ++g) {
-      float e = (j < count) ? __expf(p_s[g][j] - gmax[g]) : 0.f;
-      p_s[g][j] = e;
-      gsum[g] += e;
+  // per head: max and exp-sum over the kKeys scores (warp g handles head g)
+  float head_max = -INFINITY, head_sum = 0.f;
+  if (warp < group) {
+    float m = -INFINITY;
+    for (int j = lane; j < kKeys; j += 32) m = fmaxf(m, p_s[warp][j]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int j = lane; j < kKeys; j += 32) {
+      float e = (j < count) ? __expf(p_s[warp][j] - m) : 0.f;
+      p_s[warp][j] = e;
+      sum += e;
     }
-  for (int g = 0; g < group; ++g) {
-    float s = warp_sum(gsum[g]);
-    if (lane == 0) red[g][warp] = s;
+    head_max = m;
+    head_sum = warp_sum(sum);
   }
   __syncthreads();
+  const int d = tid & (kHeadDim - 1), parity = tid >> 7;
   float acc[kMaxGroup];
 #pragma unroll
   for (int g = 0; g < kMaxGroup; ++g) acc[g] = 0.f;
-  const __nv_bfloat16 *vbase = v_cache + (size_t(kvh) * max_len + key0) * kHeadDim + tid;
-  for (int j = 0; j < count; ++j) {
+  const __nv_bfloat16 *vbase = v_cache + (size_t(kvh) * max_len + key0) * kHeadDim + d;
+  for (int j = parity; j < count; j += 2) {
     const float v = __bfloat162float(vbase[size_t(j) * kHeadDim]);
 #pragma unroll
     for (int g = 0; g < kMaxGroup; ++g)
       if (g < group) acc[g] += p_s[g][j] * v;
   }
-  for (int g = 0; g < group; ++g) {
-    const int head = kvh * group + g;
-    float *out = partial + (size_t(head) * splits + split) * (kHeadDim + 2);
-    out[tid] = acc[g];
-    if (tid == 0) {
-      out[kHeadDim] = count > 0 ? gmax[g] : -INFINITY;
-      out[kHeadDim + 1] = red[g][0] + red[g][1] + red[g][2] + red[g][3];
+  if (parity == 1)
+    for (int g = 0; g < group; ++g) acc_s[g][d] = acc[g];
+  __syncthreads();
+  if (parity == 0)
+    for (int g = 0; g < group; ++g) {
+      float *out = partial + (size_t(kvh * group + g) * splits + split) * (kHeadDim + 2);
+      out[d] = acc[g] + acc_s[g][d];
     }
+  if (warp < group && lane == 0) {
+    float *out = partial + (size_t(kvh * group + warp) * splits + split) * (kHeadDim + 2);
+    out[kHeadDim] = count > 0 ? head_max : -INFINITY;
+    out[kHeadDim + 1] = head_sum;
   }
 }
 
@@ -218,8 +246,9 @@ using namespace tx;
 extern "C" {
 
 int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, int tokens, int hidden, float eps, void *stream) {
-  if (!h || !weight || !y || tokens < 1 || hidden < 2 || hidden % 2) return fail(TX_EINVAL, "tx_aux_add_rmsnorm: bad argument");
-  add_rmsnorm_kernel<<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  if (!h || !weight || !y || tokens < 1 || hidden < 8 || hidden % 8 || hidden > kNormThreads * 8 * kNormChunks)
+    return fail(TX_EINVAL, "tx_aux_add_rmsnorm: hidden must be a multiple of 8 and at most 16384");
+  add_rmsnorm_kernel<<<tokens, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(delta), static_cast<const __nv_bfloat16 *>(weight),
       static_cast<__nv_bfloat16 *>(y), hidden, eps);
   count_launch();
@@ -246,7 +275,7 @@ int tx_aux_attention_decode(const void *qkv, const void *k_cache, const void *v_
     return fail(TX_EUNSUPPORTED, "tx_aux_attention_decode supports head_dim 128 and up to 8 query heads per kv head");
   const int splits = (max_len + kKeys - 1) / kKeys;
   auto s = static_cast<cudaStream_t>(stream);
-  attention_partial_kernel<<<dim3(splits, kv_heads), kHeadDim, 0, s>>>(
+  attention_partial_kernel<<<dim3(splits, kv_heads), kAttnThreads, 0, s>>>(
       static_cast<const __nv_bfloat16 *>(qkv), static_cast<const __nv_bfloat16 *>(k_cache),
       static_cast<const __nv_bfloat16 *>(v_cache), static_cast<const long long *>(position), scratch, q_heads, kv_heads, max_len, scale);
   attention_combine_kernel<<<q_heads, kHeadDim, 0, s>>>(scratch, static_cast<__nv_bfloat16 *>(out), splits);

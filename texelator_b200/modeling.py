@@ -214,7 +214,7 @@ class BC4Decoder:
             self.buf_gu = torch.zeros(1, 2 * self.i_loc, **bf)
             self.buf_act = torch.zeros(1, self.i_loc, **bf)
             self.buf_down = torch.zeros(1, c.hidden, **bf)
-            self.attn_scratch = torch.zeros(q_heads * ((max_len + 255) // 256) * (c.head_dim + 2), dtype=torch.float32,
+            self.attn_scratch = torch.zeros(q_heads * ((max_len + 127) // 128) * (c.head_dim + 2), dtype=torch.float32,
                                             device=self.device)
             self.fused = c.head_dim == 128 and (c.q_heads // c.kv_heads) <= 8
         self.graph = None
