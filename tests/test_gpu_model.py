@@ -74,8 +74,9 @@ def test_fused_decode_step_matches_pytorch_glue():
         model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
         model.capture()
         assert model.launches_per_step == model.config.layers * 10 + 1
-        model.decode_graph()
-        torch.cuda.synchronize()
-        assert _cosine(model.last_hidden, hidden[0]) >= 0.9995
+        for step in range(3):      # graph replays overlap kernels (programmatic dependent launch): same results
+            model.decode_graph()
+            torch.cuda.synchronize()
+            assert _cosine(model.last_hidden, hidden[step]) >= 0.9995, step
     finally:
         model.free()

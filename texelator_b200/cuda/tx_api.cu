@@ -2,6 +2,7 @@
 // Reference counterparts: texelator/cuda/extension.cpp:7-48 (binding) and
 // texelator/cuda/texelator_cuda.cu:1260-1538 (implementation).
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -22,6 +23,13 @@ int fail(int code, const std::string &message) {
   return code;
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+bool pdl_enabled() {
+  static const bool enabled = [] {
+    const char *value = std::getenv("TEXELATOR_B200_NO_PDL");
+    return !(value && value[0] && value[0] != '0');
+  }();
+  return enabled;
+}
 
 // The scratch is sized once per device: 32 tokens * 65536 columns of scaled fp16 activations
 // for multi-token decode passes, plus their per-token multipliers.

@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16
                                                                    const __nv_bfloat16 *__restrict__ weight, __nv_bfloat16 *__restrict__ y,
                                                                    int hidden, float eps) {
   __shared__ float partial[kNormThreads / 32];
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int row = blockIdx.x, chunks = hidden / 8;
   uint4 *hr = reinterpret_cast<uint4 *>(h + size_t(row) * hidden);
   const uint4 *dr = delta ? reinterpret_cast<const uint4 *>(delta + size_t(row) * hidden) : nullptr;
@@ -34,10 +36,10 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16
   for (int c = 0; c < kNormChunks; ++c) {
     const int i = threadIdx.x + c * kNormThreads;
     if (i < chunks) {
-      uint4 v = hr[i];
+      uint4 v = __ldcg(hr + i);   // inputs come from the previous kernel: read through L2
       __nv_bfloat162 *pv = reinterpret_cast<__nv_bfloat162 *>(&v);
       if (dr) {
-        uint4 d = dr[i];
+        uint4 d = __ldcg(dr + i);
         const __nv_bfloat162 *pd = reinterpret_cast<const __nv_bfloat162 *>(&d);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -86,15 +88,17 @@ __global__ void __launch_bounds__(64) rope_append_kernel(__nv_bfloat16 *__restri
                                                          const float *__restrict__ sin_table, const long long *__restrict__ position,
                                                          __nv_bfloat16 *__restrict__ k_cache, __nv_bfloat16 *__restrict__ v_cache,
                                                          int q_heads, int kv_heads, int head_dim, int max_len) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int head = blockIdx.x, half = head_dim / 2;
-  const long long pos = *position;
+  const long long pos = __ldcg(position);
   __nv_bfloat16 *vec = qkv + size_t(head) * head_dim;
   const int i = threadIdx.x;
   if (head < q_heads + kv_heads) {
     float a = 0.f, b = 0.f;
     if (i < half) {
       const float c = cos_table[pos * half + i], s = sin_table[pos * half + i];
-      const float x1 = __bfloat162float(vec[i]), x2 = __bfloat162float(vec[i + half]);
+      const float x1 = __bfloat162float(__ldcg(vec + i)), x2 = __bfloat162float(__ldcg(vec + i + half));
       a = x1 * c - x2 * s;
       b = x2 * c + x1 * s;
       vec[i] = __float2bfloat16(a);
@@ -107,8 +111,8 @@ __global__ void __launch_bounds__(64) rope_append_kernel(__nv_bfloat16 *__restri
     }
   } else if (i < half) {
     __nv_bfloat16 *dst = v_cache + (size_t(head - q_heads - kv_heads) * max_len + pos) * head_dim;
-    dst[i] = vec[i];
-    dst[i + half] = vec[i + half];
+    dst[i] = __ldcg(vec + i);
+    dst[i + half] = __ldcg(vec + i + half);
   }
 }
 
@@ -131,7 +135,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_partial_kernel(const _
   const int split = blockIdx.x, kvh = blockIdx.y, splits = gridDim.x;
   const int group = q_heads / kv_heads;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const long long last = *position;                       // attends to keys 0..last
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const long long last = __ldcg(position);                       // attends to keys 0..last
   const int key0 = split * kKeys;
   const int count = int(max(0ll, min((long long)kKeys, last + 1 - key0)));
   // q: lane owns dimensions 4*lane .. 4*lane+3 of every query head of the group
@@ -139,7 +145,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_partial_kernel(const _
 #pragma unroll
   for (int g = 0; g < kMaxGroup; ++g) {
     if (g < group) {
-      uint2 raw = *reinterpret_cast<const uint2 *>(qkv + size_t(kvh * group + g) * kHeadDim + 4 * lane);
+      uint2 raw = __ldcg(reinterpret_cast<const uint2 *>(qkv + size_t(kvh * group + g) * kHeadDim + 4 * lane));
       float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&raw.y));
       q[g][0] = a.x * scale; q[g][1] = a.y * scale; q[g][2] = b.x * scale; q[g][3] = b.y * scale;
     } else {
@@ -151,7 +157,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_partial_kernel(const _
 #pragma unroll
     for (int g = 0; g < kMaxGroup; ++g) dot[g] = 0.f;
     if (j < count) {
-      uint2 raw = *reinterpret_cast<const uint2 *>(k_cache + (size_t(kvh) * max_len + key0 + j) * kHeadDim + 4 * lane);
+      uint2 raw = __ldcg(reinterpret_cast<const uint2 *>(k_cache + (size_t(kvh) * max_len + key0 + j) * kHeadDim + 4 * lane));
       float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&raw.y));
 #pragma unroll
       for (int g = 0; g < kMaxGroup; ++g)
@@ -187,7 +193,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_partial_kernel(const _
   for (int g = 0; g < kMaxGroup; ++g) acc[g] = 0.f;
   const __nv_bfloat16 *vbase = v_cache + (size_t(kvh) * max_len + key0) * kHeadDim + d;
   for (int j = parity; j < count; j += 2) {
-    const float v = __bfloat162float(vbase[size_t(j) * kHeadDim]);
+    const float v = __bfloat162float(__ldcg(vbase + size_t(j) * kHeadDim));
 #pragma unroll
     for (int g = 0; g < kMaxGroup; ++g)
       if (g < group) acc[g] += p_s[g][j] * v;
@@ -209,18 +215,20 @@ __global__ void __launch_bounds__(kAttnThreads) attention_partial_kernel(const _
 
 __global__ void __launch_bounds__(kHeadDim) attention_combine_kernel(const float *__restrict__ partial, __nv_bfloat16 *__restrict__ out,
                                                                      int splits) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int head = blockIdx.x, tid = threadIdx.x;
   const float *base = partial + size_t(head) * splits * (kHeadDim + 2);
   float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, base[s * (kHeadDim + 2) + kHeadDim]);
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, __ldcg(base + s * (kHeadDim + 2) + kHeadDim));
   float num = 0.f, den = 0.f;
   for (int s = 0; s < splits; ++s) {
     const float *p = base + s * (kHeadDim + 2);
-    const float pm = p[kHeadDim];
+    const float pm = __ldcg(p + kHeadDim);
     if (pm == -INFINITY) continue;
     const float w = __expf(pm - m);
-    num += w * p[tid];
-    den += w * p[kHeadDim + 1];
+    num += w * __ldcg(p + tid);
+    den += w * __ldcg(p + kHeadDim + 1);
   }
   out[size_t(head) * kHeadDim + tid] = __float2bfloat16(num / den);
 }
@@ -228,11 +236,13 @@ __global__ void __launch_bounds__(kHeadDim) attention_combine_kernel(const float
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i]
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16 *__restrict__ gu, __nv_bfloat16 *__restrict__ out,
                                                        int inter, int tokens) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int pairs = inter / 2;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < size_t(tokens) * pairs; i += size_t(gridDim.x) * blockDim.x) {
     const int t = int(i / pairs), c = int(i % pairs) * 2;
-    float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(gu + size_t(t) * 2 * inter + c));
-    float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(gu + size_t(t) * 2 * inter + inter + c));
+    float2 g = __bfloat1622float2(__ldcg(reinterpret_cast<const __nv_bfloat162 *>(gu + size_t(t) * 2 * inter + c)));
+    float2 u = __bfloat1622float2(__ldcg(reinterpret_cast<const __nv_bfloat162 *>(gu + size_t(t) * 2 * inter + inter + c)));
     // same rounding points as the PyTorch expression silu(g.float()) * u.float() -> bf16
     float a = g.x / (1.f + __expf(-g.x)) * u.x, b = g.y / (1.f + __expf(-g.y)) * u.y;
     *reinterpret_cast<__nv_bfloat162 *>(out + size_t(t) * inter + c) = __floats2bfloat162_rn(a, b);
@@ -248,9 +258,9 @@ extern "C" {
 int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, int tokens, int hidden, float eps, void *stream) {
   if (!h || !weight || !y || tokens < 1 || hidden < 8 || hidden % 8 || hidden > kNormThreads * 8 * kNormChunks)
     return fail(TX_EINVAL, "tx_aux_add_rmsnorm: hidden must be a multiple of 8 and at most 16384");
-  add_rmsnorm_kernel<<<tokens, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(delta), static_cast<const __nv_bfloat16 *>(weight),
-      static_cast<__nv_bfloat16 *>(y), hidden, eps);
+  TX_CUDA(launch_pdl(add_rmsnorm_kernel, dim3(tokens), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
+                     static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(delta),
+                     static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;
@@ -260,9 +270,10 @@ int tx_aux_rope_append(void *qkv, const float *cos_table, const float *sin_table
                        void *v_cache, int q_heads, int kv_heads, int head_dim, int max_len, void *stream) {
   if (!qkv || !cos_table || !sin_table || !position || !k_cache || !v_cache || head_dim > 128 || head_dim % 2)
     return fail(TX_EINVAL, "tx_aux_rope_append: bad argument");
-  rope_append_kernel<<<q_heads + 2 * kv_heads, 64, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16 *>(qkv), cos_table, sin_table, static_cast<const long long *>(position),
-      static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), q_heads, kv_heads, head_dim, max_len);
+  TX_CUDA(launch_pdl(rope_append_kernel, dim3(q_heads + 2 * kv_heads), dim3(64), 0, static_cast<cudaStream_t>(stream),
+                     static_cast<__nv_bfloat16 *>(qkv), cos_table, sin_table, static_cast<const long long *>(position),
+                     static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), q_heads, kv_heads,
+                     head_dim, max_len));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;
@@ -275,10 +286,12 @@ int tx_aux_attention_decode(const void *qkv, const void *k_cache, const void *v_
     return fail(TX_EUNSUPPORTED, "tx_aux_attention_decode supports head_dim 128 and up to 8 query heads per kv head");
   const int splits = (max_len + kKeys - 1) / kKeys;
   auto s = static_cast<cudaStream_t>(stream);
-  attention_partial_kernel<<<dim3(splits, kv_heads), kAttnThreads, 0, s>>>(
-      static_cast<const __nv_bfloat16 *>(qkv), static_cast<const __nv_bfloat16 *>(k_cache),
-      static_cast<const __nv_bfloat16 *>(v_cache), static_cast<const long long *>(position), scratch, q_heads, kv_heads, max_len, scale);
-  attention_combine_kernel<<<q_heads, kHeadDim, 0, s>>>(scratch, static_cast<__nv_bfloat16 *>(out), splits);
+  TX_CUDA(launch_pdl(attention_partial_kernel, dim3(splits, kv_heads), dim3(kAttnThreads), 0, s,
+                     static_cast<const __nv_bfloat16 *>(qkv), static_cast<const __nv_bfloat16 *>(k_cache),
+                     static_cast<const __nv_bfloat16 *>(v_cache), static_cast<const long long *>(position), scratch, q_heads,
+                     kv_heads, max_len, scale));
+  TX_CUDA(launch_pdl(attention_combine_kernel, dim3(q_heads), dim3(kHeadDim), 0, s, static_cast<const float *>(scratch),
+                     static_cast<__nv_bfloat16 *>(out), splits));
   count_launch(2);
   TX_CUDA(cudaGetLastError());
   return TX_OK;
@@ -288,8 +301,8 @@ int tx_aux_silu_mul(const void *gate_up, void *out, int tokens, int intermediate
   if (!gate_up || !out || tokens < 1 || intermediate < 2 || intermediate % 2) return fail(TX_EINVAL, "tx_aux_silu_mul: bad argument");
   size_t pairs = size_t(tokens) * intermediate / 2;
   int grid = int(std::min<size_t>((pairs + 255) / 256, 148 * 8));
-  silu_mul_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16 *>(gate_up),
-                                                                      static_cast<__nv_bfloat16 *>(out), intermediate, tokens);
+  TX_CUDA(launch_pdl(silu_mul_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                     static_cast<const __nv_bfloat16 *>(gate_up), static_cast<__nv_bfloat16 *>(out), intermediate, tokens));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;

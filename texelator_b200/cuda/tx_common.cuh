@@ -112,6 +112,37 @@ __device__ __forceinline__ int block_selector(unsigned long long block, int p) {
 __device__ __forceinline__ int block_e0(unsigned long long block) { return int(int8_t(block & 0xff)); }
 __device__ __forceinline__ int block_e1(unsigned long long block) { return int(int8_t((block >> 8) & 0xff)); }
 
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Kernels of the decode step are short (a few microseconds), so the
+// launch gap and the prologue of each kernel matter.  Launched with the programmatic-serialisation
+// attribute, a kernel may start while its predecessor on the stream is still draining; everything it
+// does before `grid_dependency_wait()` must therefore only read immutable data (weights, tables) and
+// write nothing outside the CTA.  `grid_dependency_wait()` returns once all earlier work on the stream
+// is complete and visible (a no-op for ordinary launches).  Data that an earlier kernel produced must
+// then be read through L2 (`__ldcg` / ld.global.cg): a CTA that started early shares its SM's L1 with
+// kernels that may have cached the old lines (observed on B200 as stale activations under CUDA-graph
+// replay).  TEXELATOR_B200_NO_PDL=1 turns the attribute off.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();
+
+template <typename... KernelArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
+}
+
 // launchers implemented in the other translation units
 int launch_retile(const uint8_t *rowmajor_dev, Handle *h, cudaStream_t stream);
 int launch_untile(const Handle *h, uint8_t *rowmajor_dev, cudaStream_t stream);

@@ -34,6 +34,7 @@ namespace tx {
 constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kMaxTokenTiles = 4;          // 8 tokens per tile
+constexpr int kXChunks = 9;                // 8-element activation chunks a thread keeps in registers while staging
 constexpr int kXsPad = 16;                 // bytes added to the shared token stride (bank spread)
 constexpr size_t kSmemBudget = 200 * 1024; // dynamic shared memory we allow one CTA to take
 
@@ -89,11 +90,12 @@ __device__ __forceinline__ uint4 convert_chunk(uint4 c, float mult) {
 __global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ xprep,
                                                                  float *__restrict__ xmul, int K, int KP) {
   __shared__ unsigned warp_max[kGemvWarps];
+  grid_dependency_wait();
   int tok = blockIdx.x;
   const uint4 *src = reinterpret_cast<const uint4 *>(x + size_t(tok) * K);
   int chunks = K / 8, padded = KP / 8;
   unsigned m = 0;
-  for (int i = threadIdx.x; i < chunks; i += kGemvThreads) m = max(m, chunk_absmax(src[i]));
+  for (int i = threadIdx.x; i < chunks; i += kGemvThreads) m = max(m, chunk_absmax(__ldcg(src + i)));
   m = __reduce_max_sync(0xffffffffu, m);
   if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
   __syncthreads();
@@ -105,7 +107,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const __nv_bfl
   if (threadIdx.x == 0) xmul[tok] = inverse * (1.0f / 889.0f);
   uint4 *dst = reinterpret_cast<uint4 *>(xprep + size_t(tok) * KP);
   for (int i = threadIdx.x; i < padded; i += kGemvThreads)
-    dst[i] = i < chunks ? convert_chunk(src[i], mult) : make_uint4(0, 0, 0, 0);
+    dst[i] = i < chunks ? convert_chunk(__ldcg(src + i), mult) : make_uint4(0, 0, 0, 0);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -162,6 +164,10 @@ gemv_tile_kernel(const GemvParams p) {
 
   fill_pair_table(lut_g, tid, kGemvThreads);
   if (tid < 16) zero_g[tid] = make_uint4(0, 0, 0, 0);
+  // Everything above touched only the immutable payload and shared memory; the activations below are
+  // produced by the previous kernel on the stream.
+  grid_launch_dependents();
+  grid_dependency_wait();
 
   // -- activations -> fp16 in shared memory
   const int chunks = p.K / 8, padded = p.KP / 8;
@@ -169,15 +175,25 @@ gemv_tile_kernel(const GemvParams p) {
     for (int tok = 0; tok < p.T; ++tok) {
       const uint4 *xp = reinterpret_cast<const uint4 *>(p.xprep + size_t(tok) * p.KP);
       uint4 *dst = reinterpret_cast<uint4 *>(xs_g + size_t(tok) * xs_stride);
-      for (int i = tid; i < padded; i += kGemvThreads) dst[i] = xp[i];
+      for (int i = tid; i < padded; i += kGemvThreads) dst[i] = __ldcg(xp + i);
     }
-    if (tid < p.T) tokmul[tid] = p.xmul[tid];
+    if (tid < p.T) tokmul[tid] = __ldcg(p.xmul + tid);
   } else {
     for (int tok = 0; tok < p.T; ++tok) {
+      // one trip to global memory: the first kXChunks*256 chunks stay in registers between the
+      // magnitude scan and the conversion (covers K <= 18432); longer rows re-read the rest
       const uint4 *xp = reinterpret_cast<const uint4 *>(p.x + size_t(tok) * p.K);
+      uint4 held[kXChunks];
       unsigned m = 0;
-#pragma unroll 4
-      for (int i = tid; i < chunks; i += kGemvThreads) m = max(m, chunk_absmax(xp[i]));
+#pragma unroll
+      for (int c = 0; c < kXChunks; ++c) {
+        const int i = tid + c * kGemvThreads;
+        if (i < chunks) {
+          held[c] = __ldcg(xp + i);   // L2 read: another kernel wrote these moments ago
+          m = max(m, chunk_absmax(held[c]));
+        }
+      }
+      for (int i = tid + kXChunks * kGemvThreads; i < chunks; i += kGemvThreads) m = max(m, chunk_absmax(__ldcg(xp + i)));
       m = __reduce_max_sync(0xffffffffu, m);
       if (lane == 0) red[warp] = m;
       __syncthreads();
@@ -188,9 +204,13 @@ gemv_tile_kernel(const GemvParams p) {
       token_scaling(m, mult, inverse);
       if (tid == 0) tokmul[tok] = inverse * (1.0f / 889.0f);
       uint4 *dst = reinterpret_cast<uint4 *>(xs_g + size_t(tok) * xs_stride);
-#pragma unroll 4
-      for (int i = tid; i < padded; i += kGemvThreads)
-        dst[i] = i < chunks ? convert_chunk(xp[i], mult) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int c = 0; c < kXChunks; ++c) {
+        const int i = tid + c * kGemvThreads;
+        if (i < padded) dst[i] = i < chunks ? convert_chunk(held[c], mult) : make_uint4(0, 0, 0, 0);
+      }
+      for (int i = tid + kXChunks * kGemvThreads; i < padded; i += kGemvThreads)
+        dst[i] = i < chunks ? convert_chunk(__ldcg(xp + i), mult) : make_uint4(0, 0, 0, 0);
       __syncthreads();
     }
   }
@@ -503,7 +523,7 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
       p.xprep = ws->xprep;
       p.xmul = ws->xmul;
     }
-    plan.kernel<<<plan.grid, kGemvThreads, plan.smem, stream>>>(p);
+    TX_CUDA(launch_pdl(plan.kernel, dim3(plan.grid), dim3(kGemvThreads), plan.smem, stream, p));
     count_launch();
   }
   TX_CUDA(cudaGetLastError());
