@@ -309,6 +309,45 @@ def run_gpu_arm(args, config) -> None:
     model.free()
 
 
+def run_micro(args) -> None:
+    """Small single-kernel case for profilers: `--micro MxK[xT]` packs enough random BC4 matrices of that
+    shape to exceed L2, runs the linear on each in turn (CUDA events) and prints one JSON line."""
+    from texelator_b200 import runtime
+    from texelator_b200.modeling import encode_minmax_cuda, software_palette_table
+    dims = [int(v) for v in args.micro.lower().split("x")]
+    m, k, tokens = dims[0], dims[1], (dims[2] if len(dims) > 2 else 1)
+    torch.cuda.set_device(0)
+    ext = runtime.extension()
+    lut = software_palette_table("cuda")
+    copies = max(2, int(200e6 // (m * k // 2)) + 1)
+    handles = []
+    for index in range(copies):
+        weight = torch.randn(m, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(index)) * 0.02
+        handles.append(ext.pack_encoded_device(*encode_minmax_cuda(weight, lut)))
+        ext.set_lookahead(handles[-1], args.lookahead)
+        ext.set_prefill_backend(handles[-1], args.backend)
+    x = torch.randn(tokens, k, device="cuda").bfloat16()
+    y = torch.empty(tokens, m, device="cuda", dtype=torch.bfloat16)
+    for _ in range(max(args.warmup, 3)):
+        for h in handles:
+            ext.linear_out(h, x, y)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.cudart().cudaProfilerStart()
+    begin.record()
+    for _ in range(args.steps):
+        for h in handles:
+            ext.linear_out(h, x, y)
+    end.record()
+    torch.cuda.synchronize()
+    torch.cuda.cudart().cudaProfilerStop()
+    us = begin.elapsed_time(end) * 1000 / (args.steps * copies)
+    bytes_per_call = m * k // 2 + 4 * m + 2 * tokens * (k + m)
+    print(json.dumps({"micro": args.micro, "copies": copies, "us_per_call": us, "GBps": bytes_per_call / us / 1e3,
+                      "TFLOPs": 2.0 * tokens * m * k / us / 1e6, "note": "eager launches: host overhead included"}), flush=True)
+    runtime.free(handles)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -319,7 +358,12 @@ def main() -> None:
     parser.add_argument("--prompt", type=int, default=2048)
     parser.add_argument("--decode", type=int, default=512)
     parser.add_argument("--lookahead", type=int, default=2)
+    parser.add_argument("--micro", default=None, help="MxK[xT]: time one linear shape alone (profiling aid)")
+    parser.add_argument("--backend", type=int, default=5, help="prefill backend id for --micro with T >= 16")
     args = parser.parse_args()
+    if args.micro:
+        run_micro(args)
+        return
     from texelator_b200.modeling import CONFIGS
     config = CONFIGS[args.model]
     if args.impl == "reference":
