@@ -326,6 +326,8 @@ def run_micro(args) -> None:
         handles.append(ext.pack_encoded_device(*encode_minmax_cuda(weight, lut)))
         ext.set_lookahead(handles[-1], args.lookahead)
         ext.set_prefill_backend(handles[-1], args.backend)
+        ext.set_palette(handles[-1], args.palette)       # throughput only: the bytes are the same either way
+        ext.set_decode_path(handles[-1], args.decode_path)
     x = torch.randn(tokens, k, device="cuda").bfloat16()
     y = torch.empty(tokens, m, device="cuda", dtype=torch.bfloat16)
     for _ in range(max(args.warmup, 3)):
@@ -358,14 +360,20 @@ def main() -> None:
     parser.add_argument("--prompt", type=int, default=2048)
     parser.add_argument("--decode", type=int, default=512)
     parser.add_argument("--lookahead", type=int, default=2)
+    parser.add_argument("--layers", type=int, default=0, help="override the layer count (profiling aid; not a bench result)")
     parser.add_argument("--micro", default=None, help="MxK[xT]: time one linear shape alone (profiling aid)")
     parser.add_argument("--backend", type=int, default=5, help="prefill backend id for --micro with T >= 16")
+    parser.add_argument("--decode-path", type=int, default=0, help="--micro: 0 mma.sync ALU decode, 1 exact ALU, 2 texture")
+    parser.add_argument("--palette", type=int, default=0, help="--micro: 0 software palette, 1 hardware (texture-unit) palette")
     args = parser.parse_args()
     if args.micro:
         run_micro(args)
         return
     from texelator_b200.modeling import CONFIGS
     config = CONFIGS[args.model]
+    if args.layers:
+        import dataclasses
+        config = dataclasses.replace(config, layers=args.layers, name=f"{config.name}-{args.layers}layers")
     if args.impl == "reference":
         run_reference_arm(args, config)
     else:

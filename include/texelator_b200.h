@@ -41,6 +41,10 @@ extern "C" {
 #define TX_DECODE_ALU_EXACT 1 /* per-weight bf16(pal*scale) with fp32 FMA, the reference's arithmetic */
 #define TX_DECODE_TEXTURE 2   /* signed-BC4 texture object + tex2Dgather, if the device offers it */
 
+/* palettes a payload can be encoded against */
+#define TX_PALETTE_SOFTWARE 0 /* exact BC4-SNORM values rounded once to fp32 (default) */
+#define TX_PALETTE_HARDWARE 1 /* what NVIDIA texture units return (the reference's published models) */
+
 /* tx_dequant output selectors */
 #define TX_DEQUANT_PALETTE_F32 0 /* unscaled palette value per weight, fp32 [M,K] */
 #define TX_DEQUANT_SCALED_F32 1  /* pal * scale_m, fp32 [M,K] */
@@ -97,8 +101,8 @@ int tx_set_prefill_backend(uint64_t handle, int backend);
 int tx_set_decode_path(uint64_t handle, int path);
 
 /* handle_info: texelator_cuda.cu:1505-1512 -> [M, K, threshold, tile_rows, backend,
- * pipelined_supported, graphics_supported]; the last two report [decode_path, lookahead] here
- * (the reference's two flags describe kernels that do not exist in this build). */
+ * pipelined_supported, graphics_supported]; the last two report [decode_path, lookahead + 16*palette]
+ * here (the reference's two flags describe kernels that do not exist in this build). */
 int tx_handle_info(uint64_t handle, int64_t out[7]);
 
 /* *_kernel_info(): texelator_cuda.cu:1514-1536, cutlass_texture_mainloop.cu:251-267 ->
@@ -115,6 +119,13 @@ int tx_free(uint64_t handle);
 int tx_palette_probe(int device, float *out_host);
 /* Same table produced by this library's ALU decoder from the same probe blocks. */
 int tx_software_palette(int device, float *out_host);
+/* New: the ALU decoder's table for TX_PALETTE_HARDWARE (closed form of the texture-unit palette; its
+ * SHA-256 is the hash the reference publishes, WINDOWS_VALIDATION.md:13-14). */
+int tx_hardware_palette(int device, float *out_host);
+/* New: declare which palette the handle's payload was encoded against (TX_PALETTE_*).  All decode
+ * paths follow it.  With TX_PALETTE_HARDWARE the texture decode path passes the palette gate on
+ * devices whose texture unit reproduces that table. */
+int tx_set_palette(uint64_t handle, int palette);
 
 /* New: exact decode of the packed device copy (TX_DEQUANT_*), for bit-exact checks against the
  * encoder's palette.  `out` is a device [M,K] array. */

@@ -52,6 +52,32 @@ def software_palette() -> np.ndarray:
     return np.where(e0 > e1, p8, p6).astype(np.float32)
 
 
+# SHA-256 of the texture-unit palette the reference publishes for RTX 4060 / 4080 SUPER / 5080
+# (WINDOWS_VALIDATION.md:13-14; research/results/paper/environment.json:32-36).
+REFERENCE_TEXTURE_PALETTE_SHA256 = "34670bd1c521c26b14ea88ed6f2d8f16c55720f20915909ac621dcabe0f3ed47"
+
+
+def hardware_palette() -> np.ndarray:
+    """The palette NVIDIA texture units produce for signed BC4 (what the reference measures with
+    texelator/cuda/texelator_cuda.cu:1540-1595 and encodes its published models against), as a
+    closed form.  Endpoints are widened to 16-bit snorm by bit replication,
+    ``X(e) = sign(e) * ((|e|<<8) | (|e|<<1) | (|e|>>6))``; interpolated entries add integer multiples
+    of ``d = e1 - e0`` to the nearer endpoint (36, 72, 144 in the 8-value mode; 48, 96 in the 6-value
+    mode); the result is ``I / 32767`` rounded to fp32.  The table reproduces the published SHA-256
+    bit for bit (``REFERENCE_TEXTURE_PALETTE_SHA256``) and equals what a B200 returns."""
+    e = np.arange(-127, 128, dtype=np.int64)
+    mag = np.abs(e)
+    wide = np.sign(e) * ((mag << 8) | (mag << 1) | (mag >> 6))
+    x0 = np.broadcast_to(wide[None, :], (255, 255))
+    x1 = np.broadcast_to(wide[:, None], (255, 255))
+    d = e[:, None] - e[None, :]
+    high = [x0, x1, x0 + 36 * d, x0 + 72 * d, x1 - 144 * d, x0 + 144 * d, x1 - 72 * d, x1 - 36 * d]
+    low = [x0, x1, x0 + 48 * d, x0 + 96 * d, x1 - 96 * d, x1 - 48 * d,
+           np.full((255, 255), -32767), np.full((255, 255), 32767)]
+    table = np.where((e[None, :] > e[:, None])[:, :, None], np.stack(high, -1), np.stack(low, -1))
+    return (table.astype(np.float64) / 32767.0).astype(np.float32)
+
+
 def palette_sha256(lut: np.ndarray) -> str:
     """SHA-256 of ``palette.bin`` (65 025 x 8 little-endian fp32) -- the value
     the reference compares in texelator/tuning.py:38-41 and

@@ -138,10 +138,17 @@ def test_lookahead_tuner_protocol(ext, lut, tmp_path, monkeypatch):
     assert [row["lookahead"] for row in profile["candidates"]] == list(tuning.CANDIDATES)
     assert all(row["max_abs_vs_k1"] <= 1e-3 for row in profile["candidates"])
     assert tuning.selected_lookahead(tmp_path / "art")[0] == profile["selected_lookahead"]
-    # palette gate: an artefact encoded against another palette is refused (texelator/tuning.py:38-41)
-    artifacts.write_artifact(tmp_path / "art", entries, "34670bd1c521c26b14ea88ed6f2d8f16c55720f20915909ac621dcabe0f3ed47")
+    # palette gate: an artefact encoded against an unknown palette is refused (texelator/tuning.py:38-41)
+    artifacts.write_artifact(tmp_path / "art", entries, "0" * 64)
     with pytest.raises(RuntimeError, match="palette does not match"):
         tuning.tune_artifact(tmp_path / "art", warmup=1, measured=1, runs=1)
+    # ... while the texture-unit palette the reference publishes is accepted where this GPU's texture
+    # unit reproduces it, and such artefacts are packed in hardware-palette mode
+    if ext.texture_supported() and O.palette_sha256(ext.palette_probe().numpy()) == O.REFERENCE_TEXTURE_PALETTE_SHA256:
+        from texelator_b200 import runtime
+        artifacts.write_artifact(tmp_path / "art", entries, O.REFERENCE_TEXTURE_PALETTE_SHA256)
+        assert runtime.palette_of(tmp_path / "art" / "weights") == runtime.PALETTE_HARDWARE
+        assert tuning.tune_artifact(tmp_path / "art", warmup=1, measured=2, runs=1)["palette_sha256"] == O.REFERENCE_TEXTURE_PALETTE_SHA256
 
 
 def test_hardware_palettes_and_texture_gate(ext, lut, tmp_path, monkeypatch):

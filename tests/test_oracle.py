@@ -26,6 +26,17 @@ def test_palette_is_pinned(lut, golden_dir):
     assert np.abs(lut).max() == 1.0
 
 
+def test_hardware_palette_reproduces_the_published_hash():
+    """Known answer of the reference: the texture-unit palette hash in WINDOWS_VALIDATION.md:13-14."""
+    table = O.hardware_palette()
+    assert table.shape == (255, 255, 8) and table.dtype == np.float32
+    assert O.palette_sha256(table) == O.REFERENCE_TEXTURE_PALETTE_SHA256
+    software = O.software_palette()
+    differ = int((table != software).sum())
+    assert differ == 453378                                   # the paper's count of differing entries (section IV-B)
+    assert abs(float(np.abs(table - software).max()) - 0.05584) < 1e-4
+
+
 def test_palette_is_monotone_between_endpoints(lut):
     order8 = [0, 2, 3, 4, 5, 6, 7, 1]
     hi = lut[0, 254][order8]                                       # e1=-127, e0=127

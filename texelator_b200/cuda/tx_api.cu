@@ -45,8 +45,8 @@ Workspace *workspace_for(int device) {
   ws.xprep_halfs = size_t(32) * 65536;
   if (status == cudaSuccess) status = cudaMalloc(&ws.xprep, ws.xprep_halfs * sizeof(__half));
   if (status == cudaSuccess) status = cudaMalloc(&ws.xmul, 64 * sizeof(float));
-  if (status == cudaSuccess) status = cudaMalloc(&ws.status, sizeof(int));
-  if (status == cudaSuccess) status = cudaMemset(ws.status, 0, sizeof(int));
+  if (status == cudaSuccess) status = cudaMalloc(&ws.status, 2 * sizeof(int));   // [0] kernel status, [1] pack-time scratch
+  if (status == cudaSuccess) status = cudaMemset(ws.status, 0, 2 * sizeof(int));
   cudaSetDevice(previous);
   if (status != cudaSuccess) {
     g_error = std::string("workspace allocation failed: ") + cudaGetErrorString(status);
@@ -255,22 +255,23 @@ int tx_set_decode_path(uint64_t handle, int path) {
     TX_CUDA(cudaSetDevice(h->device));
     // palette gate (tuning.py:38-41): the texture unit must reproduce the encoder's palette bit for bit
     static std::mutex guard;
-    static std::map<int, int> verdict;  // device -> 1 match, 0 mismatch, -1 unsupported
+    static std::map<std::pair<int, int>, int> verdict;  // (device, palette) -> 1 match, 0 mismatch, -1 unsupported
     int state;
     {
       std::lock_guard<std::mutex> lock(guard);
-      auto found = verdict.find(h->device);
+      auto key = std::make_pair(h->device, h->palette);
+      auto found = verdict.find(key);
       if (found == verdict.end()) {
         std::vector<float> hw(65025 * 8), sw(65025 * 8);
         int rc = probe_texture_palette(h->device, hw.data());
         if (rc == TX_EUNSUPPORTED) state = -1;
         else if (rc != TX_OK) { cudaSetDevice(current); return rc; }
         else {
-          rc = probe_software_palette(h->device, sw.data());
+          rc = probe_software_palette(h->device, sw.data(), h->palette);
           if (rc != TX_OK) { cudaSetDevice(current); return rc; }
           state = std::memcmp(hw.data(), sw.data(), hw.size() * sizeof(float)) == 0 ? 1 : 0;
         }
-        verdict[h->device] = state;
+        verdict[key] = state;
       } else {
         state = found->second;
       }
@@ -295,7 +296,7 @@ int tx_handle_info(uint64_t handle, int64_t out[7]) {
   out[3] = h->prefill_tile_rows;
   out[4] = h->prefill_backend;
   out[5] = h->decode_path;
-  out[6] = h->lookahead;
+  out[6] = h->lookahead + 16 * h->palette;
   return TX_OK;
 }
 
@@ -333,7 +334,22 @@ int tx_palette_probe(int device, float *out_host) {
 
 int tx_software_palette(int device, float *out_host) {
   if (!out_host) return fail(TX_EINVAL, "tx_software_palette: null output");
-  return probe_software_palette(device, out_host);
+  return probe_software_palette(device, out_host, TX_PALETTE_SOFTWARE);
+}
+
+int tx_hardware_palette(int device, float *out_host) {
+  if (!out_host) return fail(TX_EINVAL, "tx_hardware_palette: null output");
+  return probe_software_palette(device, out_host, TX_PALETTE_HARDWARE);
+}
+
+int tx_set_palette(uint64_t handle, int palette) {
+  Handle *h = as_handle(handle);
+  if (!h) return fail(TX_EINVAL, "null Texelator handle");
+  if (palette != TX_PALETTE_SOFTWARE && palette != TX_PALETTE_HARDWARE) return fail(TX_EINVAL, "unknown palette");
+  if (palette != h->palette && h->decode_path == TX_DECODE_TEXTURE)
+    return fail(TX_ESTATE, "leave the texture decode path before changing the palette");
+  h->palette = palette;
+  return TX_OK;
 }
 
 int tx_dequant(uint64_t handle, void *out, int what, void *stream_ptr) {

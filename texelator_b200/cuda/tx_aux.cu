@@ -152,21 +152,24 @@ __global__ void __launch_bounds__(kAttnThreads) attention_partial_kernel(const _
       q[g][0] = q[g][1] = q[g][2] = q[g][3] = 0.f;
     }
   }
-  for (int j = warp; j < kKeys; j += kAttnThreads / 32) {
-    float dot[kMaxGroup];
+  // all key rows of this warp are requested before any is used (16 independent 256-byte rows in flight)
+  constexpr int kPerWarp = kKeys / (kAttnThreads / 32);
+  uint2 key_raw[kPerWarp];
 #pragma unroll
-    for (int g = 0; g < kMaxGroup; ++g) dot[g] = 0.f;
-    if (j < count) {
-      uint2 raw = __ldcg(reinterpret_cast<const uint2 *>(k_cache + (size_t(kvh) * max_len + key0 + j) * kHeadDim + 4 * lane));
-      float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&raw.y));
+  for (int i = 0; i < kPerWarp; ++i) {
+    const int j = warp + i * (kAttnThreads / 32);
+    key_raw[i] = j < count ? __ldcg(reinterpret_cast<const uint2 *>(k_cache + (size_t(kvh) * max_len + key0 + j) * kHeadDim + 4 * lane))
+                           : make_uint2(0, 0);
+  }
 #pragma unroll
-      for (int g = 0; g < kMaxGroup; ++g)
-        if (g < group) dot[g] = a.x * q[g][0] + a.y * q[g][1] + b.x * q[g][2] + b.y * q[g][3];
-    }
+  for (int i = 0; i < kPerWarp; ++i) {
+    const int j = warp + i * (kAttnThreads / 32);
+    float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&key_raw[i].x));
+    float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&key_raw[i].y));
 #pragma unroll
     for (int g = 0; g < kMaxGroup; ++g)
       if (g < group) {
-        float s = warp_sum(dot[g]);
+        float s = warp_sum(a.x * q[g][0] + a.y * q[g][1] + b.x * q[g][2] + b.y * q[g][3]);
         if (lane == 0) p_s[g][j] = j < count ? s : -INFINITY;
       }
   }
@@ -192,11 +195,21 @@ __global__ void __launch_bounds__(kAttnThreads) attention_partial_kernel(const _
 #pragma unroll
   for (int g = 0; g < kMaxGroup; ++g) acc[g] = 0.f;
   const __nv_bfloat16 *vbase = v_cache + (size_t(kvh) * max_len + key0) * kHeadDim + d;
-  for (int j = parity; j < count; j += 2) {
-    const float v = __bfloat162float(__ldcg(vbase + size_t(j) * kHeadDim));
+  constexpr int kBatch = 16;                      // value rows requested together
+  for (int j0 = parity; j0 < count; j0 += 2 * kBatch) {
+    float v[kBatch];
 #pragma unroll
-    for (int g = 0; g < kMaxGroup; ++g)
-      if (g < group) acc[g] += p_s[g][j] * v;
+    for (int i = 0; i < kBatch; ++i) {
+      const int j = j0 + 2 * i;
+      v[i] = j < count ? __bfloat162float(__ldcg(vbase + size_t(j) * kHeadDim)) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int j = min(j0 + 2 * i, kKeys - 1);
+#pragma unroll
+      for (int g = 0; g < kMaxGroup; ++g)
+        if (g < group) acc[g] += p_s[g][j] * v[i];
+    }
   }
   if (parity == 1)
     for (int g = 0; g < group; ++g) acc_s[g][d] = acc[g];
@@ -217,19 +230,30 @@ __global__ void __launch_bounds__(kHeadDim) attention_combine_kernel(const float
                                                                      int splits) {
   grid_launch_dependents();
   grid_dependency_wait();
+  __shared__ float weight_s[128];
   const int head = blockIdx.x, tid = threadIdx.x;
   const float *base = partial + size_t(head) * splits * (kHeadDim + 2);
-  float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, __ldcg(base + s * (kHeadDim + 2) + kHeadDim));
-  float num = 0.f, den = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float *p = base + s * (kHeadDim + 2);
-    const float pm = __ldcg(p + kHeadDim);
-    if (pm == -INFINITY) continue;
-    const float w = __expf(pm - m);
-    num += w * __ldcg(p + tid);
-    den += w * __ldcg(p + kHeadDim + 1);
+  // thread s fetches (max, sum) of split s; the block maximum and the per-split weights go to shared memory
+  float pm = -INFINITY, pl = 0.f;
+  if (tid < splits) {
+    pm = __ldcg(base + tid * (kHeadDim + 2) + kHeadDim);
+    pl = __ldcg(base + tid * (kHeadDim + 2) + kHeadDim + 1);
   }
+  __shared__ float red_s[4];
+  float m = warp_max(pm);
+  if ((tid & 31) == 0) red_s[tid >> 5] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3]));
+  const float w = pm == -INFINITY ? 0.f : __expf(pm - m);
+  weight_s[tid] = w;
+  float den = warp_sum(w * pl);
+  __syncthreads();
+  if ((tid & 31) == 0) red_s[tid >> 5] = den;
+  __syncthreads();
+  den = red_s[0] + red_s[1] + red_s[2] + red_s[3];
+  float num = 0.f;
+#pragma unroll 8
+  for (int s = 0; s < splits; ++s) num += weight_s[s] * __ldcg(base + s * (kHeadDim + 2) + tid);
   out[size_t(head) * kHeadDim + tid] = __float2bfloat16(num / den);
 }
 
@@ -285,6 +309,7 @@ int tx_aux_attention_decode(const void *qkv, const void *k_cache, const void *v_
   if (head_dim != kHeadDim || kv_heads < 1 || q_heads % kv_heads || q_heads / kv_heads > kMaxGroup)
     return fail(TX_EUNSUPPORTED, "tx_aux_attention_decode supports head_dim 128 and up to 8 query heads per kv head");
   const int splits = (max_len + kKeys - 1) / kKeys;
+  if (splits > 128) return fail(TX_EUNSUPPORTED, "tx_aux_attention_decode supports caches of up to 16384 positions");
   auto s = static_cast<cudaStream_t>(stream);
   TX_CUDA(launch_pdl(attention_partial_kernel, dim3(splits, kv_heads), dim3(kAttnThreads), 0, s,
                      static_cast<const __nv_bfloat16 *>(qkv), static_cast<const __nv_bfloat16 *>(k_cache),

@@ -47,8 +47,10 @@ struct Handle {
   int lookahead = 2;            // texelator_cuda.cu:48 default
   int prefill_threshold = 16, prefill_tile_rows = 1024, prefill_backend = 0;
   int decode_path = TX_DECODE_ALU_MMA;
+  int palette = TX_PALETTE_SOFTWARE;   // which table the payload was encoded against
   uint8_t *tiles = nullptr;     // MT*KI*1024 bytes
   uint8_t *unit_flags = nullptr;  // MT*KI bytes: 1 if the unit holds a low-mode (e0<=e1) block
+  bool has_low_mode = false;      // any unit flag set
   float *scales = nullptr;      // M
   __nv_bfloat16 *bias = nullptr;  // M or null
   int bias_dtype = TX_DTYPE_BF16;
@@ -112,6 +114,47 @@ __device__ __forceinline__ int block_selector(unsigned long long block, int p) {
 __device__ __forceinline__ int block_e0(unsigned long long block) { return int(int8_t(block & 0xff)); }
 __device__ __forceinline__ int block_e1(unsigned long long block) { return int(int8_t((block >> 8) & 0xff)); }
 
+// Exact texture-unit ("hardware") palette, the table NVIDIA texture units return for signed BC4 and
+// the reference measures (texelator_cuda.cu:1540-1595): endpoints widened to 16-bit snorm by bit
+// replication, interpolants = nearer endpoint + {36,72,144}*(e1-e0) (8-value mode) or {48,96}*(e1-e0)
+// (6-value mode), value = I/32767 rounded to fp32 (same correctly rounded quotient trick).
+__device__ __forceinline__ int widen_snorm8(int e) {
+  int m = abs(e);
+  int w = (m << 8) | (m << 1) | (m >> 6);
+  return e < 0 ? -w : w;
+}
+__device__ __forceinline__ float hardware_palette_value(int e0, int e1, int sel) {
+  e0 = max(e0, -127);
+  e1 = max(e1, -127);
+  const int x0 = widen_snorm8(e0), x1 = widen_snorm8(e1), d = e1 - e0;
+  int v;
+  if (sel == 0) v = x0;
+  else if (sel == 1) v = x1;
+  else if (e0 > e1) {
+    switch (sel) {
+      case 2: v = x0 + 36 * d; break;
+      case 3: v = x0 + 72 * d; break;
+      case 4: v = x1 - 144 * d; break;
+      case 5: v = x0 + 144 * d; break;
+      case 6: v = x1 - 72 * d; break;
+      default: v = x1 - 36 * d; break;
+    }
+  } else {
+    switch (sel) {
+      case 2: v = x0 + 48 * d; break;
+      case 3: v = x0 + 96 * d; break;
+      case 4: v = x1 - 96 * d; break;
+      case 5: v = x1 - 48 * d; break;
+      case 6: v = -32767; break;
+      default: v = 32767; break;
+    }
+  }
+  return rn_div_const(float(v), 32767.0f, 1.0f / 32767.0f);
+}
+__device__ __forceinline__ float palette_value_of(int palette, int e0, int e1, int sel) {
+  return palette == TX_PALETTE_HARDWARE ? hardware_palette_value(e0, e1, sel) : palette_value(e0, e1, sel);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Programmatic dependent launch.  Kernels of the decode step are short (a few microseconds), so the
 // launch gap and the prologue of each kernel matter.  Launched with the programmatic-serialisation
@@ -159,6 +202,6 @@ int prefill_kernel_info(int backend, int64_t out[9]);
 int texture_supported(int device);                       // 1 / 0
 int create_texture(Handle *h);                           // builds array + BC4 view from the tiled copy
 int probe_texture_palette(int device, float *out_host);  // TX_EUNSUPPORTED when views cannot be made
-int probe_software_palette(int device, float *out_host);
+int probe_software_palette(int device, float *out_host, int palette);
 
 }  // namespace tx

@@ -49,6 +49,7 @@ struct GemvParams {
   const float *xmul;        // [T] 2^s/889 per token (PRE)
   int M, K, KI, T, MT;
   int KP;                   // KI * 128
+  int palette;              // TX_PALETTE_*
 };
 
 // amax of |x| over one token row, as the integer order of bf16 magnitudes
@@ -117,7 +118,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const __nv_bfl
 // combine their fp32 partial tiles through shared memory (double-buffered, one named barrier per
 // tile).  No global scratch, no atomics, deterministic summation order.
 // ------------------------------------------------------------------------------------------
-template <int LOOKAHEAD, int NT, bool PRE>
+template <int LOOKAHEAD, int NT, bool PRE, bool LOWMODE>
 __global__ void __launch_bounds__(kGemvThreads, (NT == 1 && LOOKAHEAD <= 2) ? 3 : (NT <= 2 ? 2 : 1))
 gemv_tile_kernel(const GemvParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -134,35 +135,41 @@ gemv_tile_kernel(const GemvParams p) {
   const unsigned xs_s = lut_s + kLutBytes + 512 + kPartBytes;
   const unsigned xs_stride = unsigned(p.KP) * 2 + kXsPad;
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // same value, but known to be warp-uniform
   const int g = lane >> 2, t = lane & 3;
   const int KI = p.KI, MT = p.MT;
   const int WS = KI < kGemvWarps ? KI : kGemvWarps;   // warps that own column units
   const bool worker = warp < WS;
+  const int per_tile = worker ? (KI - warp + WS - 1) / WS : 0;   // units of this warp in every tile
 
-  // -- first loads, issued before anything else.  Prefetch addresses past the last tile fall back
-  //    to the first unit (valid memory, never consumed).
+  // -- first loads, issued before anything else.  The prefetch pointer walks this warp's units
+  //    (ki = warp, warp + WS, ... of tiles blockIdx.x, + gridDim.x, ...) and stops at the end of the payload.
   const int tile_stride = gridDim.x;
-  int ptile = blockIdx.x, pk = warp;
+  const long long first_unit = (long long)blockIdx.x * KI + warp;
+  const uint4 *pnext = p.tiles + first_unit * 64 + lane;
+  const uint8_t *fnext = p.flags + first_unit;
+  const uint4 *const plimit = p.tiles + (long long)MT * KI * 64;
+  const long long step_unit = WS, step_tile = (long long)tile_stride * KI - (long long)(per_tile - 1) * WS;
+  int pcount = 0;
   uint4 pend[LOOKAHEAD][2];
   unsigned pflag[LOOKAHEAD];
   auto prefetch = [&](int slot) {
-    const bool live = worker && ptile < MT;
-    const long long unit = live ? (long long)ptile * KI + pk : 0;
-    const uint4 *src = p.tiles + unit * 64 + lane;
-    pend[slot][0] = ldg_stream(src);
-    pend[slot][1] = ldg_stream(src + 32);
-    pflag[slot] = p.flags[unit];
-    pk += WS;
-    if (pk >= KI) {
-      pk = warp;
-      ptile += tile_stride;
+    if (worker && pnext < plimit) {
+      pend[slot][0] = ldg_stream(pnext);
+      pend[slot][1] = ldg_stream(pnext + 32);
+      pflag[slot] = *fnext;
     }
+    const bool wrap = pcount == per_tile - 1;
+    const long long advance = wrap ? step_tile : step_unit;
+    pnext += advance * 64;
+    fnext += advance;
+    pcount = wrap ? 0 : pcount + 1;
   };
 #pragma unroll
   for (int i = 0; i < LOOKAHEAD; ++i) prefetch(i);
 
-  fill_pair_table(lut_g, tid, kGemvThreads);
+  fill_pair_table(lut_g, tid, kGemvThreads, p.palette);
   if (tid < 16) zero_g[tid] = make_uint4(0, 0, 0, 0);
   // Everything above touched only the immutable payload and shared memory; the activations below are
   // produced by the previous kernel on the stream.
@@ -233,12 +240,15 @@ gemv_tile_kernel(const GemvParams p) {
   constexpr int kElems = NT * 128;
   constexpr int kPerThread = (kElems + 31) / 32;   // upper bound (one worker warp)
   float row_scale[kPerThread], row_bias[kPerThread];
+  bool row_live[kPerThread];   // this thread's element exists (row < M, token < T)
   auto load_row_constants = [&](int rt) {
 #pragma unroll
     for (int j = 0; j < kPerThread; ++j) {
       int e = tid + j * workers;
       int row = rt * 16 + ((e >> 6) & 1) * 8 + ((e & 31) >> 2);
-      bool ok = e < kElems && row < p.M;
+      int tok = (e >> 7) * 8 + 2 * (e & 3) + ((e >> 5) & 1);
+      bool ok = e < kElems && row < p.M && tok < p.T;
+      row_live[j] = ok;
       row_scale[j] = ok ? p.scales[row] : 0.f;
       row_bias[j] = ok && p.bias ? __bfloat162float(p.bias[row]) : 0.f;
     }
@@ -251,7 +261,7 @@ gemv_tile_kernel(const GemvParams p) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) acc[nt][q] = acc2[nt][q] = 0.f;
 
-  int tile = blockIdx.x, ki = warp, buf = 0;
+  int tile = blockIdx.x, done = 0, buf = 0;
   unsigned xoff = unsigned(warp) * 256;
   const unsigned xoff_step = unsigned(WS) * 256;
   load_row_constants(tile);
@@ -266,12 +276,11 @@ gemv_tile_kernel(const GemvParams p) {
         const unsigned qlo = sub ? q.z : q.x, qhi = sub ? q.w : q.y;
         const unsigned rlo = sub ? r.z : r.x, rhi = sub ? r.w : r.y;
         unsigned aq[8], ar[8];
-        if (flag) {
-          if (block_is_low(qlo)) decode_block_slow(qlo, qhi, aq); else decode_block_fast(qlo, qhi, lut_lane, aq);
-          if (block_is_low(rlo)) decode_block_slow(rlo, rhi, ar); else decode_block_fast(rlo, rhi, lut_lane, ar);
-        } else {
-          decode_block_fast(qlo, qhi, lut_lane, aq);
-          decode_block_fast(rlo, rhi, lut_lane, ar);
+        decode_block_fast(qlo, qhi, lut_lane, aq);
+        decode_block_fast(rlo, rhi, lut_lane, ar);
+        if (LOWMODE && __any_sync(0xffffffffu, flag != 0)) {   // rare, warp-uniform: redo the low-mode blocks
+          if (block_is_low(qlo)) decode_block_slow(qlo, qhi, aq, p.palette);
+          if (block_is_low(rlo)) decode_block_slow(rlo, rhi, ar, p.palette);
         }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -284,9 +293,8 @@ gemv_tile_kernel(const GemvParams p) {
         }
       }
       prefetch(slot);   // refill the slot only now: its registers are free, so no copies are needed
-      ki += WS;
       xoff += xoff_step;
-      if (ki >= KI) {
+      if (++done == per_tile) {
         // ---- this warp's share of the tile is done: publish the partial, combine, store
         float *mine = part_g + (buf * kGemvWarps + warp) * kElems + lane;
 #pragma unroll
@@ -300,21 +308,20 @@ gemv_tile_kernel(const GemvParams p) {
 #pragma unroll
         for (int j = 0; j < kPerThread; ++j) {
           const int e = tid + j * workers;
-          if (e < kElems) {
+          if (row_live[j]) {
             const float *src = part_g + buf * kGemvWarps * kElems + e;
             float sum = 0.f;
             for (int w = 0; w < WS; ++w) sum += src[w * kElems];
             const int c = e >> 5, ln = e & 31;
             const int row = tile * 16 + ((c >> 1) & 1) * 8 + (ln >> 2);
             const int tok = (c >> 2) * 8 + 2 * (ln & 3) + (c & 1);
-            if (row < p.M && tok < p.T)
-              p.y[size_t(tok) * p.M + row] = __float2bfloat16(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j]));
+            p.y[size_t(tok) * p.M + row] = __float2bfloat16(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j]));
           }
         }
         buf ^= 1;
         tile += tile_stride;
         if (tile >= MT) return;
-        ki = warp;
+        done = 0;
         xoff = unsigned(warp) * 256;
         load_row_constants(tile);
       }
@@ -330,7 +337,7 @@ __global__ void __launch_bounds__(256) gemv_exact_kernel(const unsigned long lon
                                                          const float *__restrict__ scales,
                                                          const __nv_bfloat16 *__restrict__ bias,
                                                          const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y,
-                                                         int M, int K, int bpr, int KI) {
+                                                         int M, int K, int bpr, int KI, int palette) {
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int row = blockIdx.x * 8 + warp, token = blockIdx.y;
   if (row >= M) return;
@@ -342,8 +349,8 @@ __global__ void __launch_bounds__(256) gemv_exact_kernel(const unsigned long lon
     int e0 = block_e0(block), e1 = block_e1(block);
 #pragma unroll
     for (int p = 0; p < 16; p += 2) {
-      float w0 = __bfloat162float(__float2bfloat16(__fmul_rn(palette_value(e0, e1, block_selector(block, p)), scale)));
-      float w1 = __bfloat162float(__float2bfloat16(__fmul_rn(palette_value(e0, e1, block_selector(block, p + 1)), scale)));
+      float w0 = __bfloat162float(__float2bfloat16(__fmul_rn(palette_value_of(palette, e0, e1, block_selector(block, p)), scale)));
+      float w1 = __bfloat162float(__float2bfloat16(__fmul_rn(palette_value_of(palette, e0, e1, block_selector(block, p + 1)), scale)));
       a0 = fmaf(w0, __bfloat162float(x[kb * 16 + p]), a0);
       a1 = fmaf(w1, __bfloat162float(x[kb * 16 + p + 1]), a1);
     }
@@ -359,7 +366,7 @@ int launch_gemv_exact(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y,
     dim3 grid((h->M + 7) / 8, n);
     gemv_exact_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const unsigned long long *>(h->tiles), h->scales, h->bias,
                                                 x + size_t(t0) * h->K, y + size_t(t0) * h->M, h->M, h->K,
-                                                h->blocks_per_row, h->KI);
+                                                h->blocks_per_row, h->KI, h->palette);
     count_launch();
   }
   TX_CUDA(cudaGetLastError());
@@ -416,25 +423,33 @@ int launch_gemv_texture(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *
 // ------------------------------------------------------------------------------------------
 using GemvKernel = void (*)(const GemvParams);
 
-template <int NT, bool PRE>
+// Kernel variants: LOOKAHEAD x token tiles x activation source x "payload has low-mode blocks".
+// Matrices without a single low-mode block (the normal case for dense weights) run a variant that
+// carries no generic-decode code at all.
+template <int NT, bool PRE, bool LOWMODE>
 static GemvKernel pick_lookahead(int lookahead) {
   switch (lookahead) {
-    case 1: return gemv_tile_kernel<1, NT, PRE>;
-    case 2: return gemv_tile_kernel<2, NT, PRE>;
-    case 3: return gemv_tile_kernel<3, NT, PRE>;
-    case 4: return gemv_tile_kernel<4, NT, PRE>;
-    case 6: return gemv_tile_kernel<6, NT, PRE>;
-    default: return gemv_tile_kernel<8, NT, PRE>;
+    case 1: return gemv_tile_kernel<1, NT, PRE, LOWMODE>;
+    case 2: return gemv_tile_kernel<2, NT, PRE, LOWMODE>;
+    case 3: return gemv_tile_kernel<3, NT, PRE, LOWMODE>;
+    case 4: return gemv_tile_kernel<4, NT, PRE, LOWMODE>;
+    case 6: return gemv_tile_kernel<6, NT, PRE, LOWMODE>;
+    default: return gemv_tile_kernel<8, NT, PRE, LOWMODE>;
   }
 }
 
-static GemvKernel pick_kernel(int lookahead, int nt, bool pre) {
-  if (!pre) return pick_lookahead<1, false>(lookahead);
+template <bool LOWMODE>
+static GemvKernel pick_tokens(int lookahead, int nt, bool pre) {
+  if (!pre) return pick_lookahead<1, false, LOWMODE>(lookahead);
   switch (nt) {
-    case 1: return pick_lookahead<1, true>(lookahead);
-    case 2: return pick_lookahead<2, true>(lookahead);
-    default: return pick_lookahead<4, true>(lookahead);
+    case 1: return pick_lookahead<1, true, LOWMODE>(lookahead);
+    case 2: return pick_lookahead<2, true, LOWMODE>(lookahead);
+    default: return pick_lookahead<4, true, LOWMODE>(lookahead);
   }
+}
+
+static GemvKernel pick_kernel(int lookahead, int nt, bool pre, bool low_mode) {
+  return low_mode ? pick_tokens<true>(lookahead, nt, pre) : pick_tokens<false>(lookahead, nt, pre);
 }
 
 static size_t gemv_smem_bytes(int KP, int tokens, int nt) {
@@ -467,7 +482,7 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan) {
   plan.nt = token_tiles(tokens);
   // in-CTA activation conversion only while it stays a short prologue
   plan.pre = !(tokens <= 2 && size_t(tokens) * h->K <= 36864);
-  plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre);
+  plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre, h->has_low_mode);
   plan.smem = gemv_smem_bytes(KP, tokens, plan.nt);
   // attribute + occupancy queries are cached per (device, kernel, shared bytes)
   static std::mutex guard;
@@ -515,6 +530,7 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
     p.MT = h->MT;
     p.T = n;
     p.KP = KP;
+    p.palette = h->palette;
     if (plan.pre) {
       // scaled fp16 activations go through the per-device scratch (one pre-pass CTA per token)
       if (size_t(n) * KP > ws->xprep_halfs) return fail(TX_EINVAL, "tokens*K exceeds the activation scratch of the decode GEMV");
@@ -586,7 +602,7 @@ int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfl
   StaticScratch *scratch = nullptr;
   int rc = static_scratch_for(h->device, &scratch);
   if (rc != TX_OK) return rc;
-  GemvKernel kernel = pick_kernel(h->lookahead, nt, true);
+  GemvKernel kernel = pick_kernel(h->lookahead, nt, true, h->has_low_mode);
   TX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
   int per_sm = 0;
   TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem));
@@ -604,6 +620,7 @@ int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfl
   p.MT = h->MT;
   p.T = tokens;
   p.KP = KP;
+  p.palette = h->palette;
   p.xprep = scratch->activations;
   p.xmul = scratch->multipliers;
   gemv_xprep_kernel<<<tokens, kGemvThreads, 0, stream>>>(x, scratch->activations, scratch->multipliers, h->K, KP);
@@ -617,7 +634,7 @@ int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfl
 
 int gemv_kernel_info(int64_t out[9]) {
   cudaFuncAttributes attributes{};
-  GemvKernel kernel = gemv_tile_kernel<2, 1, false>;
+  GemvKernel kernel = gemv_tile_kernel<2, 1, false, false>;
   TX_CUDA(cudaFuncGetAttributes(&attributes, kernel));
   TX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
   int active = 0;

@@ -41,6 +41,12 @@ __global__ void untile_kernel(const unsigned long long *__restrict__ tiles, unsi
   }
 }
 
+__global__ void any_flag_kernel(const uint8_t *__restrict__ flags, size_t units, int *__restrict__ result) {
+  int seen = 0;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < units; i += size_t(gridDim.x) * blockDim.x) seen |= flags[i];
+  if (__any_sync(0xffffffffu, seen) && (threadIdx.x & 31) == 0) atomicOr(result, 1);
+}
+
 int launch_retile(const uint8_t *rowmajor_dev, Handle *h, cudaStream_t stream) {
   size_t units = size_t(h->MT) * h->KI;
   TX_CUDA(cudaMemsetAsync(h->unit_flags, 0, units, stream));
@@ -51,6 +57,16 @@ int launch_retile(const uint8_t *rowmajor_dev, Handle *h, cudaStream_t stream) {
                                           h->blocks_per_row, h->MT, h->KI);
   count_launch();
   TX_CUDA(cudaGetLastError());
+  // does the payload contain any low-mode block at all?  (decides the decode kernel variant)
+  Workspace *ws = workspace_for(h->device);
+  if (!ws) return TX_ECUDA;
+  TX_CUDA(cudaMemsetAsync(ws->status + 1, 0, sizeof(int), stream));
+  any_flag_kernel<<<int(std::min<size_t>((units + 255) / 256, 592)), 256, 0, stream>>>(h->unit_flags, units, ws->status + 1);
+  count_launch();
+  int any = 0;
+  TX_CUDA(cudaMemcpyAsync(&any, ws->status + 1, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  TX_CUDA(cudaStreamSynchronize(stream));
+  h->has_low_mode = any != 0;
   return TX_OK;
 }
 
@@ -71,7 +87,7 @@ int launch_untile(const Handle *h, uint8_t *rowmajor_dev, cudaStream_t stream) {
 // ------------------------------------------------------------------------------------------
 template <int WHAT>
 __global__ void dequant_kernel(const unsigned long long *__restrict__ tiles, const float *__restrict__ scales,
-                               void *__restrict__ out, int M, int bpr, int KI) {
+                               void *__restrict__ out, int M, int bpr, int KI, int palette) {
   size_t total = size_t(M) * bpr;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
     int row = int(i / bpr), kb = int(i % bpr);
@@ -81,7 +97,7 @@ __global__ void dequant_kernel(const unsigned long long *__restrict__ tiles, con
     float v[16];
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
-      float pal = palette_value(e0, e1, block_selector(block, p));
+      float pal = palette_value_of(palette, e0, e1, block_selector(block, p));
       v[p] = WHAT == TX_DEQUANT_PALETTE_F32 ? pal : __fmul_rn(pal, scale);
     }
     size_t base = size_t(row) * bpr * 16 + size_t(kb) * 16;
@@ -106,13 +122,13 @@ int launch_dequant(const Handle *h, void *out, int what, cudaStream_t stream) {
   auto tiles = reinterpret_cast<const unsigned long long *>(h->tiles);
   switch (what) {
     case TX_DEQUANT_PALETTE_F32:
-      dequant_kernel<TX_DEQUANT_PALETTE_F32><<<grid, 128, 0, stream>>>(tiles, h->scales, out, h->M, h->blocks_per_row, h->KI);
+      dequant_kernel<TX_DEQUANT_PALETTE_F32><<<grid, 128, 0, stream>>>(tiles, h->scales, out, h->M, h->blocks_per_row, h->KI, h->palette);
       break;
     case TX_DEQUANT_SCALED_F32:
-      dequant_kernel<TX_DEQUANT_SCALED_F32><<<grid, 128, 0, stream>>>(tiles, h->scales, out, h->M, h->blocks_per_row, h->KI);
+      dequant_kernel<TX_DEQUANT_SCALED_F32><<<grid, 128, 0, stream>>>(tiles, h->scales, out, h->M, h->blocks_per_row, h->KI, h->palette);
       break;
     case TX_DEQUANT_SCALED_BF16:
-      dequant_kernel<TX_DEQUANT_SCALED_BF16><<<grid, 128, 0, stream>>>(tiles, h->scales, out, h->M, h->blocks_per_row, h->KI);
+      dequant_kernel<TX_DEQUANT_SCALED_BF16><<<grid, 128, 0, stream>>>(tiles, h->scales, out, h->M, h->blocks_per_row, h->KI, h->palette);
       break;
     default:
       return fail(TX_EINVAL, "tx_dequant: unknown output selector");
@@ -138,14 +154,15 @@ static void build_probe_blocks(std::vector<unsigned long long> &host) {
     }
 }
 
-__global__ void software_palette_kernel(const unsigned long long *__restrict__ blocks, float *__restrict__ out, int pairs) {
+__global__ void software_palette_kernel(const unsigned long long *__restrict__ blocks, float *__restrict__ out, int pairs,
+                                        int palette) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= pairs) return;
   unsigned long long block = blocks[i];
-  for (int s = 0; s < 8; ++s) out[size_t(i) * 8 + s] = palette_value(block_e0(block), block_e1(block), block_selector(block, s));
+  for (int s = 0; s < 8; ++s) out[size_t(i) * 8 + s] = palette_value_of(palette, block_e0(block), block_e1(block), block_selector(block, s));
 }
 
-int probe_software_palette(int device, float *out_host) {
+int probe_software_palette(int device, float *out_host, int palette) {
   TX_CUDA(cudaSetDevice(device));
   constexpr int pairs = 255 * 255;
   std::vector<unsigned long long> host;
@@ -155,7 +172,7 @@ int probe_software_palette(int device, float *out_host) {
   TX_CUDA(cudaMalloc(&blocks, size_t(pairs) * 8));
   TX_CUDA(cudaMalloc(&out, size_t(pairs) * 8 * sizeof(float)));
   TX_CUDA(cudaMemcpy(blocks, host.data(), size_t(pairs) * 8, cudaMemcpyHostToDevice));
-  software_palette_kernel<<<(pairs + 255) / 256, 256>>>(blocks, out, pairs);
+  software_palette_kernel<<<(pairs + 255) / 256, 256>>>(blocks, out, pairs, palette);
   count_launch();
   cudaError_t status = cudaGetLastError();
   if (status == cudaSuccess) status = cudaMemcpy(out_host, out, size_t(pairs) * 8 * sizeof(float), cudaMemcpyDeviceToHost);

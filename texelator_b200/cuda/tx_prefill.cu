@@ -59,6 +59,7 @@ struct PrefillParams {
   __nv_bfloat16 *y;
   int *status;
   int M, K, KI, MT, T;
+  int palette;
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -126,11 +127,11 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned 
 }
 
 // Exact software-palette numerators scaled to the high-mode denominator, for blocks in the low mode.
-__device__ __forceinline__ void decode_block_low_f32(unsigned lo, unsigned hi, float (&v)[16]) {
+__device__ __forceinline__ void decode_block_low_f32(unsigned lo, unsigned hi, float (&v)[16], int palette) {
   unsigned long long block = (unsigned long long)lo | ((unsigned long long)hi << 32);
   int e0 = block_e0(block), e1 = block_e1(block);
 #pragma unroll
-  for (int p = 0; p < 16; ++p) v[p] = palette_value(e0, e1, block_selector(block, p)) * 889.0f;
+  for (int p = 0; p < 16; ++p) v[p] = palette_value_of(palette, e0, e1, block_selector(block, p)) * 889.0f;
 }
 
 template <int BN>
@@ -165,7 +166,7 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  fill_pair_table(lut_g, tid, kPrefillThreads);
+  fill_pair_table(lut_g, tid, kPrefillThreads, p.palette);
   if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bars_s + 208), "r"(unsigned(BN)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -211,7 +212,7 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
           unsigned packed[8];
           if (cflag && block_is_low(lo)) {
             float v[16];
-            decode_block_low_f32(lo, hi, v);
+            decode_block_low_f32(lo, hi, v, p.palette);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               __nv_bfloat162 w = __floats2bfloat162_rn(v[2 * i] * rs[half], v[2 * i + 1] * rs[half]);
@@ -374,6 +375,7 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
   p.KI = h->KI;
   p.MT = h->MT;
   p.T = tokens;
+  p.palette = h->palette;
   dim3 grid((h->M + kBM - 1) / kBM, (tokens + BN - 1) / BN);
   prefill_umma_kernel<BN><<<grid, kPrefillThreads, TileConfig<BN>::smem, stream>>>(p, map);
   count_launch();

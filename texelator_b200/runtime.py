@@ -34,6 +34,7 @@ PREFILL_TILE_ROWS = int(os.environ.get("TEXELATOR_PREFILL_TILE_ROWS", "1024"))
 DTYPE_F16, DTYPE_BF16 = 0, 1
 DECODE_ALU_MMA, DECODE_ALU_EXACT, DECODE_TEXTURE = 0, 1, 2
 DEQUANT_PALETTE_F32, DEQUANT_SCALED_F32, DEQUANT_SCALED_BF16 = 0, 1, 2
+PALETTE_SOFTWARE, PALETTE_HARDWARE = 0, 1
 TX_EUNSUPPORTED = -3
 
 # every symbol include/texelator_b200.h declares: name -> (restype, argtypes)
@@ -56,6 +57,8 @@ C_API = {
     "tx_free": (_i32, [_u64]),
     "tx_palette_probe": (_i32, [_i32, _vp]),
     "tx_software_palette": (_i32, [_i32, _vp]),
+    "tx_hardware_palette": (_i32, [_i32, _vp]),
+    "tx_set_palette": (_i32, [_u64, _i32]),
     "tx_dequant": (_i32, [_u64, _vp, _i32, _vp]),
     "tx_unpack_blocks": (_i32, [_u64, _vp]),
     "tx_kernel_status": (_i32, [_i32, _i32]),
@@ -256,6 +259,16 @@ class _Extension:
         self._check(self._lib.tx_software_palette(torch.cuda.current_device(), out.data_ptr()))
         return out
 
+    def hardware_palette(self) -> torch.Tensor:
+        """The ALU decoder's table for the texture-unit palette (closed form)."""
+        out = torch.empty((255 * 255, 8), dtype=torch.float32)
+        self._check(self._lib.tx_hardware_palette(torch.cuda.current_device(), out.data_ptr()))
+        return out
+
+    def set_palette(self, handle: int, palette: int) -> None:
+        """Declare the palette the handle's payload was encoded against (``PALETTE_*``)."""
+        self._check(self._lib.tx_set_palette(handle, int(palette)))
+
     def texture_supported(self) -> bool:
         return bool(self.runtime_info()[3])
 
@@ -388,8 +401,20 @@ def pack_entry(weights: Path, entry: dict, bias: torch.Tensor | None = None, loo
     return handle
 
 
+def palette_of(weights: Path) -> int:
+    """Which palette the artefact under ``weights`` was encoded against, from the ``palette_sha256`` its
+    ``metadata.json`` records (texelator/converter.py:204): the published texture-unit hash selects
+    ``PALETTE_HARDWARE``, anything else the software palette (the tuner's gate still checks the hash)."""
+    from .hardware import REFERENCE_TEXTURE_PALETTE_SHA256
+    try:
+        recorded = json.loads((Path(weights) / "metadata.json").read_text()).get("palette_sha256")
+    except (OSError, ValueError):
+        recorded = None
+    return PALETTE_HARDWARE if recorded == REFERENCE_TEXTURE_PALETTE_SHA256 else PALETTE_SOFTWARE
+
+
 def pack_entry_handles(weights: Path, entry: dict, bias: torch.Tensor | None = None, lookahead: int = 1,
-                       max_texture_rows: int = 32768) -> list[int]:
+                       max_texture_rows: int = 32768, palette: int | None = None) -> list[int]:
     """Pack one matrix, splitting very tall outputs into independent handles
     (texelator/runtime.py:179-207; the reference needs the split for the texture height limit,
     it is kept so handle lists look the same)."""
@@ -400,6 +425,7 @@ def pack_entry_handles(weights: Path, entry: dict, bias: torch.Tensor | None = N
     raw_blocks = np.memmap(weights / entry["blocks_file"], dtype=np.uint8, mode="r", shape=(m, row_bytes))
     raw_scales = np.memmap(weights / entry["scales_file"], dtype="<f4", mode="r", shape=(m,))
     ext = extension()
+    palette = palette_of(weights) if palette is None else palette
     handles: list[int] = []
     try:
         for start in range(0, m, max_texture_rows):
@@ -409,6 +435,7 @@ def pack_entry_handles(weights: Path, entry: dict, bias: torch.Tensor | None = N
             handle = ext.pack_encoded(block_tensor, scale_tensor, bias[start:stop] if bias is not None else None)
             ext.set_lookahead(handle, lookahead)
             ext.set_prefill(handle, PREFILL_THRESHOLD, PREFILL_TILE_ROWS)
+            ext.set_palette(handle, palette)
             handles.append(handle)
     except Exception:
         free(handles)

@@ -16,7 +16,7 @@ from pathlib import Path
 import torch
 
 from .artifacts import safe_name, sha256_file, state_home, write_json
-from .hardware import ensure_hardware
+from .hardware import REFERENCE_TEXTURE_PALETTE_SHA256, ensure_hardware
 from .runtime import extension, free, pack_entry_handles
 
 CANDIDATES = (1, 2, 3, 4, 6, 8)
@@ -39,7 +39,13 @@ def tune_artifact(artifact: Path, warmup: int = 10, measured: int = 50, runs: in
         raise RuntimeError(f"unsupported Texelator runtime dtype: {runtime_dtype_name!r} (this build runs bfloat16 artefacts)")
     current_palette = ensure_hardware()
     expected_palette = manifest.get("hardware", {}).get("palette_sha256")
-    if not expected_palette or sha256_file(current_palette) != expected_palette:
+    # the artefact must be encoded against a palette this GPU's decoder reproduces: the software
+    # palette, or the texture-unit palette when this device's texture unit returns exactly that table
+    accepted = {sha256_file(current_palette)}
+    texture_table = current_palette.with_name("texture_palette.bin")
+    if texture_table.exists() and sha256_file(texture_table) == REFERENCE_TEXTURE_PALETTE_SHA256:
+        accepted.add(REFERENCE_TEXTURE_PALETTE_SHA256)
+    if not expected_palette or expected_palette not in accepted:
         raise RuntimeError("model BC4 palette does not match this GPU; benchmark aborted")
     weights = artifact / manifest["weights"]
     metadata_path = weights / "metadata.json"
