@@ -31,8 +31,9 @@ bool pdl_enabled() {
   return enabled;
 }
 
-// The scratch is sized once per device: 32 tokens * 65536 columns of scaled fp16 activations
-// for multi-token decode passes, plus their per-token multipliers.
+// The scratch is sized once per device: 48 Mi scaled fp16 activations (96 MiB; multi-token decode
+// passes use the first 32 tokens' worth, the prefill GEMM stages whole token chunks) plus one
+// multiplier per staged token.
 Workspace *workspace_for(int device) {
   std::lock_guard<std::mutex> lock(g_workspace_guard);
   auto found = g_workspaces.find(device);
@@ -42,9 +43,9 @@ Workspace *workspace_for(int device) {
   Workspace ws;
   cudaError_t status = cudaSetDevice(device);
   if (status == cudaSuccess) status = cudaDeviceGetAttribute(&ws.sm_count, cudaDevAttrMultiProcessorCount, device);
-  ws.xprep_halfs = size_t(32) * 65536;
+  ws.xprep_halfs = size_t(48) << 20;
   if (status == cudaSuccess) status = cudaMalloc(&ws.xprep, ws.xprep_halfs * sizeof(__half));
-  if (status == cudaSuccess) status = cudaMalloc(&ws.xmul, 64 * sizeof(float));
+  if (status == cudaSuccess) status = cudaMalloc(&ws.xmul, 65536 * sizeof(float));
   if (status == cudaSuccess) status = cudaMalloc(&ws.status, 2 * sizeof(int));   // [0] kernel status, [1] pack-time scratch
   if (status == cudaSuccess) status = cudaMemset(ws.status, 0, 2 * sizeof(int));
   cudaSetDevice(previous);

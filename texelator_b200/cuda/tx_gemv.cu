@@ -632,6 +632,14 @@ int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfl
   return TX_OK;
 }
 
+// Shared by the prefill GEMM: rescaled fp16 activations [tokens, KP] + per-token multipliers 2^s/889.
+int launch_activation_prepass(const __nv_bfloat16 *x, __half *out, float *multipliers, int tokens, int K, int KP, cudaStream_t stream) {
+  gemv_xprep_kernel<<<tokens, kGemvThreads, 0, stream>>>(x, out, multipliers, K, KP);
+  count_launch();
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
 int gemv_kernel_info(int64_t out[9]) {
   cudaFuncAttributes attributes{};
   GemvKernel kernel = gemv_tile_kernel<2, 1, false, false>;

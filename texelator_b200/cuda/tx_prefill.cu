@@ -5,15 +5,22 @@
 // (texelator/cuda/cutlass_texture_mainloop.cu:61-249, _t1/_t2/_t3/_smalln.cu; sm_80 mma.sync,
 // two-stage register-staged pipeline).  B200 design, one CTA per 128 output rows x BN tokens:
 //
+//   pre-pass   one small kernel rescales the activations per token by an exact power of two and stores
+//              them as fp16 (the decode GEMV's staging), so that both operands are fp16;
 //   warps 0-7  producers: 128-bit loads of the tiled BC4 payload (one 16-row tile per warp), decode
-//              in registers exactly like the decode GEMV (pair table + HFMA2 -> integer numerators),
-//              scale by scale_m/889 in fp32, round once to bf16 and store the 128 x 128 A tile into
-//              shared memory in the canonical K-major core-matrix layout (no swizzle);
-//   warp 8     one lane issues the TMA load of the X tile (BN tokens x 128 columns) per stage through
-//              a 3-D tensor map that lands in the same core-matrix layout (no multicast);
-//   warp 9     allocates TMEM, and one lane issues eight tcgen05.mma (M=128, N=BN, K=16) per stage,
-//              committing to the stage's "empty" barrier;
-//   warps 0-7  epilogue: tcgen05.ld of the fp32 accumulators, + bias, one bf16 rounding, store.
+//              in registers exactly like the decode GEMV (pair table + HFMA2 -> exact integer
+//              numerators n = 7*e0 + g*(e1-e0) as fp16) and store the 128 x 128 A tile into shared
+//              memory in the canonical K-major core-matrix layout (no swizzle);
+//   warp 8     one lane issues the TMA load of the staged X tile (BN tokens x 128 columns) per stage
+//              through a 3-D tensor map that lands in the same core-matrix layout (no multicast);
+//   warp 9     allocates TMEM, and one lane issues eight tcgen05.mma kind::f16 (M=128, N=BN, K=16) per
+//              stage, committing to the stage's "empty" barrier;
+//   warps 0-7  epilogue: tcgen05.ld of the fp32 accumulators, * scale_m * 2^s/889, + bias, one bf16
+//              rounding, store.
+//
+// Numerics are those of the decode GEMV: products of exact integers and exactly rescaled activations,
+// fp32 accumulation, weights never rounded to bf16 (the reference rounds bf16(pal*scale); the outputs
+// differ by that rounding only, rel-RMS about 1e-3).
 //
 // Output rows are the MMA M (TMEM lanes) and tokens the MMA N (TMEM columns), so every weight tile
 // is decoded once per CTA for all BN tokens.  K is consumed in the same 16-column steps and the
@@ -56,6 +63,7 @@ struct PrefillParams {
   const uint8_t *flags;
   const float *scales;
   const __nv_bfloat16 *bias;
+  const float *xmul;   // per-token multiplier 2^s/889 of the staged activations
   __nv_bfloat16 *y;
   int *status;
   int M, K, KI, MT, T;
@@ -126,14 +134,6 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned 
          ((unsigned long long)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
 }
 
-// Exact software-palette numerators scaled to the high-mode denominator, for blocks in the low mode.
-__device__ __forceinline__ void decode_block_low_f32(unsigned lo, unsigned hi, float (&v)[16], int palette) {
-  unsigned long long block = (unsigned long long)lo | ((unsigned long long)hi << 32);
-  int e0 = block_e0(block), e1 = block_e1(block);
-#pragma unroll
-  for (int p = 0; p < 16; ++p) v[p] = palette_value_of(palette, e0, e1, block_selector(block, p)) * 889.0f;
-}
-
 template <int BN>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x_map) {
@@ -182,12 +182,6 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
     const int rt = blockIdx.x * (kBM / 16) + warp;       // this warp's 16-row tile
     const bool live = rt < p.MT;
     const unsigned lut_lane = lut_s + lane * 4;
-    float rs[2];
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      int row = rt * 16 + half * 8 + g;
-      rs[half] = (live && row < p.M) ? p.scales[row] * (1.0f / 889.0f) : 0.f;
-    }
     const uint4 *src = p.tiles + (size_t(live ? rt : 0) * p.KI) * 64 + lane;
     const uint8_t *fl = p.flags + size_t(live ? rt : 0) * p.KI;
     uint4 q = ldg_stream(src), r = ldg_stream(src + 32);
@@ -210,24 +204,8 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
         for (int sub = 0; sub < 2; ++sub) {
           const unsigned lo = sub ? u.z : u.x, hi = sub ? u.w : u.y;
           unsigned packed[8];
-          if (cflag && block_is_low(lo)) {
-            float v[16];
-            decode_block_low_f32(lo, hi, v, p.palette);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              __nv_bfloat162 w = __floats2bfloat162_rn(v[2 * i] * rs[half], v[2 * i + 1] * rs[half]);
-              packed[i] = *reinterpret_cast<unsigned *>(&w);
-            }
-          } else {
-            unsigned a[8];
-            decode_block_fast(lo, hi, lut_lane, a);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              float2 n = __half22float2(*reinterpret_cast<__half2 *>(&a[i]));
-              __nv_bfloat162 w = __floats2bfloat162_rn(n.x * rs[half], n.y * rs[half]);
-              packed[i] = *reinterpret_cast<unsigned *>(&w);
-            }
-          }
+          decode_block_fast(lo, hi, lut_lane, packed);          // exact integer numerators as fp16x2
+          if (cflag && block_is_low(lo)) decode_block_slow(lo, hi, packed, p.palette);
           // block kb = sub*4 + t of the stage -> K chunks 2kb, 2kb+1; row = warp*16 + half*8 + g
           uint8_t *dst = stage + (2 * (sub * 4 + t)) * kALbo + (warp * 2 + half) * kASbo + g * 16;
           *reinterpret_cast<uint4 *>(dst) = live ? make_uint4(packed[0], packed[1], packed[2], packed[3]) : make_uint4(0, 0, 0, 0);
@@ -258,7 +236,8 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
   } else {
     // ---------------- MMA issue ----------------
     if (lane == 0) {
-      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | (unsigned(BN >> 3) << 17) | (unsigned(kBM >> 4) << 24);
+      // D = f32 (bits 4-5 = 1), A = B = f16 (format 0), both K-major, N at bit 17, M at bit 24
+      const unsigned idesc = (1u << 4) | (unsigned(BN >> 3) << 17) | (unsigned(kBM >> 4) << 24);
       bool ok = true;
       for (int kt = 0; kt < KT && ok; ++kt) {
         const int s = kt % S;
@@ -286,6 +265,7 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
       const int quarter = warp & 3;
       const int row = row0 + quarter * 32 + lane;
       const float bias = (row < p.M && p.bias) ? __bfloat162float(p.bias[row]) : 0.f;
+      const float row_scale = row < p.M ? p.scales[row] : 0.f;
       for (int c = warp >> 2; c < BN / 32; c += 2) {
         unsigned v[32];
         tmem_load32(tmem_base + (unsigned(quarter * 32) << 16) + unsigned(c * 32), v);
@@ -293,7 +273,8 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int tok = tok0 + c * 32 + j;
-            if (tok < p.T) p.y[size_t(tok) * p.M + row] = __float2bfloat16(__uint_as_float(v[j]) + bias);
+            if (tok < p.T)
+              p.y[size_t(tok) * p.M + row] = __float2bfloat16(fmaf(__uint_as_float(v[j]), row_scale * __ldg(p.xmul + tok), bias));
           }
         }
       }
@@ -353,32 +334,43 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
       configured[h->device] = true;
     }
   }
-  // X viewed as [K/8 chunks][T tokens][8 elements]: one box lands as BN-token core-matrix columns
-  CUtensorMap map;
-  cuuint64_t dims[3] = {8, cuuint64_t(tokens), cuuint64_t(h->K / 8)};
-  cuuint64_t strides[2] = {cuuint64_t(h->K) * 2, 16};
-  cuuint32_t box[3] = {8, cuuint32_t(BN), cuuint32_t(kChunks)};
-  cuuint32_t elem[3] = {1, 1, 1};
-  CUresult rc = encode_tiled_entry()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16 *>(x), dims, strides,
-                                     box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) return fail(TX_ECUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(rc)));
-  PrefillParams p{};
-  p.tiles = reinterpret_cast<const uint4 *>(h->tiles);
-  p.flags = h->unit_flags;
-  p.scales = h->scales;
-  p.bias = h->bias;
-  p.y = y;
-  p.status = ws->status;
-  p.M = h->M;
-  p.K = h->K;
-  p.KI = h->KI;
-  p.MT = h->MT;
-  p.T = tokens;
-  p.palette = h->palette;
-  dim3 grid((h->M + kBM - 1) / kBM, (tokens + BN - 1) / BN);
-  prefill_umma_kernel<BN><<<grid, kPrefillThreads, TileConfig<BN>::smem, stream>>>(p, map);
-  count_launch();
+  // Activations are staged once as fp16 after an exact per-token power-of-two rescale (the decode GEMV's
+  // arithmetic), in chunks of tokens that fit the per-device scratch.
+  const int KP = h->KI * 128;
+  const int chunk_tokens = int(std::min<size_t>(std::min<size_t>(ws->xprep_halfs / size_t(KP), 65536), size_t(tokens)));
+  if (chunk_tokens < 1) return fail(TX_EINVAL, "K is too large for the prefill activation scratch");
+  for (int t0 = 0; t0 < tokens; t0 += chunk_tokens) {
+    const int n = std::min(chunk_tokens, tokens - t0);
+    int rc = launch_activation_prepass(x + size_t(t0) * h->K, ws->xprep, ws->xmul, n, h->K, KP, stream);
+    if (rc != TX_OK) return rc;
+    // staged X viewed as [KP/8 chunks][n tokens][8 elements]: one box lands as BN-token core-matrix columns
+    CUtensorMap map;
+    cuuint64_t dims[3] = {8, cuuint64_t(n), cuuint64_t(KP / 8)};
+    cuuint64_t strides[2] = {cuuint64_t(KP) * 2, 16};
+    cuuint32_t box[3] = {8, cuuint32_t(BN), cuuint32_t(kChunks)};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult cr = encode_tiled_entry()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, ws->xprep, dims, strides, box, elem,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(TX_ECUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(cr)));
+    PrefillParams p{};
+    p.tiles = reinterpret_cast<const uint4 *>(h->tiles);
+    p.flags = h->unit_flags;
+    p.scales = h->scales;
+    p.bias = h->bias;
+    p.xmul = ws->xmul;
+    p.y = y + size_t(t0) * h->M;
+    p.status = ws->status;
+    p.M = h->M;
+    p.K = h->K;
+    p.KI = h->KI;
+    p.MT = h->MT;
+    p.T = n;
+    p.palette = h->palette;
+    dim3 grid((h->M + kBM - 1) / kBM, (n + BN - 1) / BN);
+    prefill_umma_kernel<BN><<<grid, kPrefillThreads, TileConfig<BN>::smem, stream>>>(p, map);
+    count_launch();
+  }
   TX_CUDA(cudaGetLastError());
   return TX_OK;
 }
