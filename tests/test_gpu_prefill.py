@@ -30,7 +30,7 @@ def _pack(ext, blocks, scales, bias=None):
     return ext.pack_encoded(torch.from_numpy(blocks), torch.from_numpy(scales), bias)
 
 
-@pytest.mark.parametrize("backend", [5, 6, 7, 8])
+@pytest.mark.parametrize("backend", [5, 6, 7, 8, 9])
 @pytest.mark.parametrize("m,k,tokens", [(128, 128, 32), (256, 512, 40), (200, 48, 17), (1024, 1024, 128),
                                         (136, 2064, 300), (5120, 640, 512)])
 def test_prefill_tiles_match_oracle(ext, lut, backend, m, k, tokens):
@@ -57,7 +57,7 @@ def test_prefill_tiles_are_bitwise_identical(ext, lut):
     try:
         ext.set_prefill(h, 1, 32768)
         outs = []
-        for backend in (5, 6, 7, 8):
+        for backend in (5, 6, 7, 8, 9):
             ext.set_prefill_backend(h, backend)
             outs.append(ext.linear(h, x.cuda()))
         for other in outs[1:]:
@@ -111,7 +111,7 @@ def test_kernel_info_and_autotune_protocol(ext, lut, tmp_path, monkeypatch):
     assert profile["status"] == "complete" and len(profile["selections"]) == 4
     for record in profile["selections"].values():
         assert record["correctness_vs_baseline"][autotune.BASELINE]["bitwise_equal"]
-        assert "stream_16x8x128" in record["rejected"] or record["correctness_vs_baseline"]["stream_16x8x128"]["bitwise_equal"]
+        assert not record["rejected"]                          # every tile is bitwise identical to the baseline
     handles = []
     try:
         from texelator_b200 import runtime

@@ -8,9 +8,9 @@ events (:170-193); the winner per ``"tokens<=B:M=m:K=k"`` key is stored together
 facts, device facts and a hash of the kernel sources (:194-242); ``apply_profile`` refuses a
 profile made for another build or GPU (:247-258).
 
-The candidates are this build's sm_100a tiles: the tcgen05 kernel with 256/128/64/32 tokens per
-CTA (ids 5-8) and the streamed mma.sync path (id 9), which uses different arithmetic and is
-therefore expected to be rejected by the bitwise gate -- it stays listed so the gate is exercised.
+The candidates are this build's sm_100a tiles of one tcgen05 kernel (output rows x tokens x columns
+per pipeline stage): 128x256x128 (baseline), 256x256x64, 512x128x64, 128x64x128, 128x32x128.  All of
+them consume K in the same 16-column steps, so they pass the bitwise gate against each other.
 Unlike the reference, ``apply_profile`` leaves the prefill threshold alone, so single-token decode
 keeps the decode GEMV after a profile was applied.
 """
@@ -30,10 +30,10 @@ from .runtime import extension, free, pack_entry_handles
 
 CANDIDATES = {
     "umma_128x256x128": 5,
-    "umma_128x128x128": 6,
-    "umma_128x64x128": 7,
-    "umma_128x32x128": 8,
-    "stream_16x8x128": 9,
+    "umma_256x256x64": 6,
+    "umma_512x128x64": 7,
+    "umma_128x64x128": 8,
+    "umma_128x32x128": 9,
 }
 BASELINE = "umma_128x256x128"
 TOKEN_BUCKETS = (32, 128, 512, 2048, 8192, 16384, 32768, 65535)

@@ -192,7 +192,6 @@ int launch_untile(const Handle *h, uint8_t *rowmajor_dev, cudaStream_t stream);
 int launch_dequant(const Handle *h, void *out, int what, cudaStream_t stream);
 int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
-int launch_activation_prepass(const __nv_bfloat16 *x, __half *out, float *multipliers, int tokens, int K, int KP, cudaStream_t stream);
 int launch_gemv_exact(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_gemv_texture(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_prefill_tile(const Handle *h, int backend, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens,

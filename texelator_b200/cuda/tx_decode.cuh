@@ -100,6 +100,40 @@ __device__ __forceinline__ bool block_is_low(unsigned lo) {
   return int(int8_t(lo & 0xff)) <= int(int8_t((lo >> 8) & 0xff));
 }
 
+// amax of |x| over one token row, as the integer order of bf16 magnitudes
+__device__ __forceinline__ unsigned chunk_absmax(uint4 c) {
+  unsigned m = 0;
+  unsigned w[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m = max(m, w[i] & 0x7fffu);
+    m = max(m, (w[i] >> 16) & 0x7fffu);
+  }
+  return m;
+}
+
+// power-of-two scaling that brings a row with bf16 magnitude pattern `amax_bits` below 2^15
+__device__ __forceinline__ void token_scaling(unsigned amax_bits, float &mult, float &inverse) {
+  int ex = int(amax_bits >> 7) & 0xff;
+  if (amax_bits == 0) ex = 141;
+  ex = min(max(ex, 15), 254);
+  mult = __int_as_float((268 - ex) << 23);      // 2^(14 - (ex-127))
+  inverse = __int_as_float((ex - 14) << 23);    // 2^((ex-127) - 14)
+}
+
+__device__ __forceinline__ uint4 convert_chunk(uint4 c, float mult) {
+  unsigned w[4] = {c.x, c.y, c.z, c.w};
+  unsigned o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float lo = __uint_as_float(w[i] << 16) * mult;
+    float hi = __uint_as_float(w[i] & 0xffff0000u) * mult;
+    __half2 h = __floats2half2_rn(lo, hi);
+    o[i] = *reinterpret_cast<unsigned *>(&h);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // Selector-pair table: entry idx holds fp16x2 (g(idx & 7), g(idx >> 3)), replicated for every lane so
 // that bank == lane.  g is the interpolation position of the high palette mode in sevenths:
 // software palette 0,7,1,2,3,4,5,6 (exact integers, so n = 7*e0 + g*(e1-e0) is exact in fp16);

@@ -52,40 +52,6 @@ struct GemvParams {
   int palette;              // TX_PALETTE_*
 };
 
-// amax of |x| over one token row, as the integer order of bf16 magnitudes
-__device__ __forceinline__ unsigned chunk_absmax(uint4 c) {
-  unsigned m = 0;
-  unsigned w[4] = {c.x, c.y, c.z, c.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    m = max(m, w[i] & 0x7fffu);
-    m = max(m, (w[i] >> 16) & 0x7fffu);
-  }
-  return m;
-}
-
-// power-of-two scaling that brings a row with bf16 magnitude pattern `amax_bits` below 2^15
-__device__ __forceinline__ void token_scaling(unsigned amax_bits, float &mult, float &inverse) {
-  int ex = int(amax_bits >> 7) & 0xff;
-  if (amax_bits == 0) ex = 141;
-  ex = min(max(ex, 15), 254);
-  mult = __int_as_float((268 - ex) << 23);      // 2^(14 - (ex-127))
-  inverse = __int_as_float((ex - 14) << 23);    // 2^((ex-127) - 14)
-}
-
-__device__ __forceinline__ uint4 convert_chunk(uint4 c, float mult) {
-  unsigned w[4] = {c.x, c.y, c.z, c.w};
-  unsigned o[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float lo = __uint_as_float(w[i] << 16) * mult;
-    float hi = __uint_as_float(w[i] & 0xffff0000u) * mult;
-    __half2 h = __floats2half2_rn(lo, hi);
-    o[i] = *reinterpret_cast<unsigned *>(&h);
-  }
-  return make_uint4(o[0], o[1], o[2], o[3]);
-}
-
 // Pre-pass for larger token counts: one CTA per token writes scaled fp16 activations and the
 // per-token multiplier 2^s/889 to scratch.
 __global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ xprep,
@@ -627,14 +593,6 @@ int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfl
   count_launch();
   const int grid = std::max(1, std::min(h->MT, scratch->sm_count * std::min(per_sm, 3)));
   kernel<<<grid, kGemvThreads, smem, stream>>>(p);
-  count_launch();
-  TX_CUDA(cudaGetLastError());
-  return TX_OK;
-}
-
-// Shared by the prefill GEMM: rescaled fp16 activations [tokens, KP] + per-token multipliers 2^s/889.
-int launch_activation_prepass(const __nv_bfloat16 *x, __half *out, float *multipliers, int tokens, int K, int KP, cudaStream_t stream) {
-  gemv_xprep_kernel<<<tokens, kGemvThreads, 0, stream>>>(x, out, multipliers, K, KP);
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;

@@ -3,19 +3,19 @@
 //
 // Reference counterpart: the five CUTLASS 2.x tiles whose B iterator gathers BC4 texels
 // (texelator/cuda/cutlass_texture_mainloop.cu:61-249, _t1/_t2/_t3/_smalln.cu; sm_80 mma.sync,
-// two-stage register-staged pipeline).  B200 design, one CTA per 128 output rows x BN tokens:
+// two-stage register-staged pipeline).  B200 design, one CTA per MT*128 output rows x BN tokens:
 //
 //   pre-pass   one small kernel rescales the activations per token by an exact power of two and stores
-//              them as fp16 (the decode GEMV's staging), so that both operands are fp16;
-//   warps 0-7  producers: 128-bit loads of the tiled BC4 payload (one 16-row tile per warp), decode
-//              in registers exactly like the decode GEMV (pair table + HFMA2 -> exact integer
-//              numerators n = 7*e0 + g*(e1-e0) as fp16) and store the 128 x 128 A tile into shared
+//              them as fp16 (the decode GEMV's staging) in the chunk-major order of the B operand;
+//   warps 0-15 producers: 128-bit loads of the tiled BC4 payload (one 8-row half of a 16-row tile per
+//              warp), decode in registers exactly like the decode GEMV (pair table + HFMA2 -> exact
+//              integer numerators n = 7*e0 + g*(e1-e0) as fp16) and store the A tile into shared
 //              memory in the canonical K-major core-matrix layout (no swizzle);
-//   warp 8     one lane issues the TMA load of the staged X tile (BN tokens x 128 columns) per stage
-//              through a 3-D tensor map that lands in the same core-matrix layout (no multicast);
-//   warp 9     allocates TMEM, and one lane issues eight tcgen05.mma kind::f16 (M=128, N=BN, K=16) per
-//              stage, committing to the stage's "empty" barrier;
-//   warps 0-7  epilogue: tcgen05.ld of the fp32 accumulators, * scale_m * 2^s/889, + bias, one bf16
+//   warp 16    one lane issues the TMA load of the staged X tile (BN tokens x BK columns) per stage
+//              through a 3-D tensor map whose rows are 512 contiguous bytes (no multicast);
+//   warp 17    allocates TMEM, and one lane issues MT * BK/16 tcgen05.mma kind::f16 (M=128, N=BN, K=16)
+//              per stage, committing to the stage's "empty" barrier;
+//   warps 0-15 epilogue: tcgen05.ld of the fp32 accumulators, * scale_m * 2^s/889, + bias, one bf16
 //              rounding, store.
 //
 // Numerics are those of the decode GEMV: products of exact integers and exactly rescaled activations,
@@ -41,21 +41,34 @@
 
 namespace tx {
 
-constexpr int kBM = 128;                 // output rows per CTA (TMEM lanes)
-constexpr int kBK = 128;                 // columns per stage = one unit of the tiled payload
-constexpr int kChunks = kBK / 8;         // 16-byte K chunks (core-matrix columns) per stage
-constexpr int kALbo = 2064;              // byte stride between K chunks of the A tile (2048 + 16: bank spread)
-constexpr int kASbo = 128;               // byte stride between 8-row groups
-constexpr int kAStage = kChunks * kALbo; // 33024
-constexpr int kProducerWarps = 8;
-constexpr int kPrefillThreads = 320;     // 8 producer/epilogue warps + TMA warp + MMA warp
+constexpr int kMmaM = 128;               // rows of one tcgen05.mma (TMEM lanes)
+constexpr int kASbo = 128;               // byte stride between 8-row groups of the A tile
+constexpr int kProducerWarps = 16;              // 8: one 16-row tile per warp; 16: one 8-row half of a tile per warp
+constexpr int kTileWarps = 8;                   // 16-row tiles of one 128-row accumulator
+constexpr int kHalvesPerWarp = 16 / kProducerWarps;
+constexpr int kTmaWarp = kProducerWarps, kMmaWarp = kProducerWarps + 1;
+constexpr int kPrefillThreads = (kProducerWarps + 2) * 32;   // producer/epilogue warps + TMA warp + MMA warp
+static_assert(kProducerWarps == 8 || kProducerWarps == 16, "producer warps split tiles whole or by halves");
 constexpr unsigned kSpinLimit = 1u << 22;
 
-template <int BN> struct TileConfig {
-  static constexpr int stages = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
-  static constexpr int b_stage = BN * kBK * 2;
+// One tile shape: MT x 128 output rows (MT accumulators side by side in TMEM), BN tokens, BK columns
+// per pipeline stage.  Per FLOP the X tile is re-read 1/(128*MT) times, so tall tiles relieve L2; the
+// BC4 side costs a quarter of a byte per weight either way.
+template <int MT, int BN, int BK> struct TileConfig {
+  static constexpr int rows = MT * kMmaM;
+  static constexpr int chunks = BK / 8;                       // 16-byte K chunks per stage
+  static constexpr int a_lbo = MT * 16 * kASbo + 16;          // chunk stride (+16: conflict-free stores)
+  static constexpr int a_stage = chunks * a_lbo;
   static constexpr int b_lbo = BN * 16;
-  static constexpr size_t smem = 1024 /*align*/ + kLutBytes * 2 + 256 /*barriers*/ + size_t(stages) * (kAStage + b_stage);
+  static constexpr int b_stage = chunks * b_lbo;
+  static constexpr int fixed = 1024 /*align*/ + kLutBytes * 2 + 256 /*barriers*/;
+  static constexpr int fit = (220 * 1024 - fixed) / (a_stage + b_stage);
+  static constexpr int stages = fit > 4 ? 4 : fit;
+  static constexpr size_t smem = fixed + size_t(stages) * (a_stage + b_stage);
+  static constexpr int tmem_columns = MT * BN;
+  static_assert(stages >= 2, "tile does not fit two pipeline stages");
+  static_assert(BN % 32 == 0, "the activation box is made of 32-token runs");
+  static_assert(tmem_columns <= 512 && (tmem_columns & (tmem_columns - 1)) == 0, "TMEM columns must be a power of two <= 512");
 };
 
 struct PrefillParams {
@@ -134,11 +147,50 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned 
          ((unsigned long long)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
 }
 
-template <int BN>
+// Activation staging for the GEMM: per token an exact power-of-two rescale to fp16 (the decode GEMV's
+// arithmetic), stored chunk-major -- out[(chunk * padded_tokens + token) * 8 .. +8], padded_tokens a
+// multiple of 32 -- which is the K-major core-matrix order of the B operand.  A TMA box then copies
+// runs of 32 tokens x 16 bytes = 512 contiguous bytes; with the row-major layout every 16-byte piece
+// was a TMA row of its own and the load, not the tensor pipe, set the pace of the wide tiles.
+// One CTA of 1024 threads stages eight tokens: four warps find the scaling of each token, then all
+// threads convert and write 128-byte runs (eight tokens of one chunk).
+constexpr int kStageThreads = 1024;
+__global__ void __launch_bounds__(kStageThreads) stage_activations_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ out,
+                                                                          float *__restrict__ xmul, int K, int KP, int tokens,
+                                                                          int padded_tokens) {
+  __shared__ unsigned warp_max[32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunks = K / 8, padded = KP / 8;
+  const int first = blockIdx.x * 8;
+  {
+    const int tok = first + (warp >> 2);
+    unsigned m = 0;
+    if (tok < tokens) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(x + size_t(tok) * K);
+      for (int i = (warp & 3) * 32 + lane; i < chunks; i += 128) m = max(m, chunk_absmax(src[i]));
+      m = __reduce_max_sync(0xffffffffu, m);
+    }
+    if (lane == 0) warp_max[warp] = m;
+  }
+  __syncthreads();
+  const int j = threadIdx.x & 7, tok = first + j;
+  const unsigned m = max(max(warp_max[4 * j], warp_max[4 * j + 1]), max(warp_max[4 * j + 2], warp_max[4 * j + 3]));
+  float mult, inverse;
+  token_scaling(m, mult, inverse);
+  if (threadIdx.x < 8 && tok < tokens) xmul[tok] = inverse * (1.0f / 889.0f);
+  uint4 *dst = reinterpret_cast<uint4 *>(out);
+  const uint4 *src = reinterpret_cast<const uint4 *>(x + size_t(tok < tokens ? tok : 0) * K);
+  for (int chunk = threadIdx.x >> 3; chunk < padded; chunk += kStageThreads / 8)
+    dst[size_t(chunk) * padded_tokens + tok] =
+        (tok < tokens && chunk < chunks) ? convert_chunk(src[chunk], mult) : make_uint4(0, 0, 0, 0);
+}
+
+template <int MT, int BN, int BK>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x_map) {
-  using Cfg = TileConfig<BN>;
+  using Cfg = TileConfig<MT, BN, BK>;
   constexpr int S = Cfg::stages;
+  constexpr int kSubs = 128 / BK;            // pipeline stages per 128-column unit of the payload (1 or 2)
   extern __shared__ uint8_t smem_raw[];
   const unsigned sbase = unsigned(__cvta_generic_to_shared(smem_raw));
   const unsigned lut_s = (sbase + kLutBytes - 1) & ~unsigned(kLutBytes - 1);
@@ -150,11 +202,11 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
   unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars_g + 208);
   const unsigned tiles_s = (bars_s + 256 + 1023) & ~1023u;   // A stages then B stages, 1 KiB aligned
   uint8_t *tiles_g = smem_raw + (tiles_s - sbase);
-  const unsigned a_s = tiles_s, b_s = tiles_s + S * kAStage;
+  const unsigned a_s = tiles_s, b_s = tiles_s + S * Cfg::a_stage;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int KT = p.KI;                                   // stages of 128 columns
-  const int row0 = blockIdx.x * kBM, tok0 = blockIdx.y * BN;
+  const int KT = p.KI * kSubs;                           // pipeline stages over K
+  const int row0 = blockIdx.x * Cfg::rows, tok0 = blockIdx.y * BN;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -167,8 +219,8 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   fill_pair_table(lut_g, tid, kPrefillThreads, p.palette);
-  if (warp == 9) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bars_s + 208), "r"(unsigned(BN)) : "memory");
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bars_s + 208), "r"(unsigned(Cfg::tmem_columns)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -177,54 +229,86 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
   const unsigned tmem_base = *tmem_slot;
 
   if (warp < kProducerWarps) {
-    // ---------------- producers: BC4 -> bf16 A tile ----------------
+    // ---------------- producers: BC4 -> fp16 A tile; warp w owns 16-row tiles w, w+8, ... of the CTA ----------------
     const int g = lane >> 2, t = lane & 3;
-    const int rt = blockIdx.x * (kBM / 16) + warp;       // this warp's 16-row tile
-    const bool live = rt < p.MT;
     const unsigned lut_lane = lut_s + lane * 4;
-    const uint4 *src = p.tiles + (size_t(live ? rt : 0) * p.KI) * 64 + lane;
-    const uint8_t *fl = p.flags + size_t(live ? rt : 0) * p.KI;
-    uint4 q = ldg_stream(src), r = ldg_stream(src + 32);
-    unsigned flag = fl[0];
-    for (int kt = 0; kt < KT; ++kt) {
-      const int s = kt % S;
-      const uint4 cq = q, cr = r;
-      const unsigned cflag = flag;
-      if (kt + 1 < KT) {                                 // next unit in flight while this one is decoded
-        q = ldg_stream(src + size_t(kt + 1) * 64);
-        r = ldg_stream(src + size_t(kt + 1) * 64 + 32);
-        flag = fl[kt + 1];
-      }
-      if (kt >= S && !mbar_wait(empty + 8 * s, ((kt / S) - 1) & 1, abort_flag, p.status, 1)) break;
-      uint8_t *stage = tiles_g + s * kAStage;
+    const int tile_warp = warp % kTileWarps, half0 = warp / kTileWarps;   // half0 is 0 with eight producers
+    const uint4 *src[MT];
+    const uint8_t *fl[MT];
+    bool live[MT];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const uint4 u = half ? cr : cq;
+    for (int m = 0; m < MT; ++m) {
+      const int rt = blockIdx.x * (Cfg::rows / 16) + m * kTileWarps + tile_warp;
+      live[m] = rt < p.MT;
+      src[m] = p.tiles + (size_t(live[m] ? rt : 0) * p.KI) * 64 + half0 * 32 + lane;
+      fl[m] = p.flags + size_t(live[m] ? rt : 0) * p.KI;
+    }
+    uint4 q[MT][kHalvesPerWarp];
+    unsigned flag[MT];
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-          const unsigned lo = sub ? u.z : u.x, hi = sub ? u.w : u.y;
-          unsigned packed[8];
-          decode_block_fast(lo, hi, lut_lane, packed);          // exact integer numerators as fp16x2
-          if (cflag && block_is_low(lo)) decode_block_slow(lo, hi, packed, p.palette);
-          // block kb = sub*4 + t of the stage -> K chunks 2kb, 2kb+1; row = warp*16 + half*8 + g
-          uint8_t *dst = stage + (2 * (sub * 4 + t)) * kALbo + (warp * 2 + half) * kASbo + g * 16;
-          *reinterpret_cast<uint4 *>(dst) = live ? make_uint4(packed[0], packed[1], packed[2], packed[3]) : make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4 *>(dst + kALbo) = live ? make_uint4(packed[4], packed[5], packed[6], packed[7]) : make_uint4(0, 0, 0, 0);
+    for (int m = 0; m < MT; ++m) {
+#pragma unroll
+      for (int h = 0; h < kHalvesPerWarp; ++h) q[m][h] = ldg_stream(src[m] + h * 32);
+      flag[m] = fl[m][0];
+    }
+    bool ok = true;
+    for (int unit = 0; unit < p.KI && ok; ++unit) {
+      uint4 cq[MT][kHalvesPerWarp];
+      unsigned cflag[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        cflag[m] = flag[m];
+#pragma unroll
+        for (int h = 0; h < kHalvesPerWarp; ++h) cq[m][h] = q[m][h];
+        if (unit + 1 < p.KI) {                           // next unit in flight while this one is decoded
+#pragma unroll
+          for (int h = 0; h < kHalvesPerWarp; ++h) q[m][h] = ldg_stream(src[m] + size_t(unit + 1) * 64 + h * 32);
+          flag[m] = fl[m][unit + 1];
         }
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor core
-      __syncwarp();
-      if (lane == 0) mbar_arrive(full_a + 8 * s);
+#pragma unroll
+      for (int part = 0; part < kSubs; ++part) {
+        const int kt = unit * kSubs + part, s = kt % S;
+        if (kt >= S && !mbar_wait(empty + 8 * s, ((kt / S) - 1) & 1, abort_flag, p.status, 1)) {
+          ok = false;
+          break;
+        }
+        uint8_t *stage = tiles_g + s * Cfg::a_stage;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+#pragma unroll
+          for (int h = 0; h < kHalvesPerWarp; ++h) {
+            const uint4 u = cq[m][h];
+            const int half = half0 + h;
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+              if (kSubs == 2 && sub != part) continue;   // 64-column stages take one block column of the unit each
+              const unsigned lo = sub ? u.z : u.x, hi = sub ? u.w : u.y;
+              unsigned packed[8];
+              decode_block_fast(lo, hi, lut_lane, packed);          // exact integer numerators as fp16x2
+              if (cflag[m] && block_is_low(lo)) decode_block_slow(lo, hi, packed, p.palette);
+              // block kb of the stage -> K chunks 2kb, 2kb+1; row = (m*8 + tile_warp)*16 + half*8 + g
+              const int kb = (kSubs == 2 ? 0 : sub * 4) + t;
+              uint8_t *dst = stage + (2 * kb) * Cfg::a_lbo + ((m * kTileWarps + tile_warp) * 2 + half) * kASbo + g * 16;
+              *reinterpret_cast<uint4 *>(dst) = live[m] ? make_uint4(packed[0], packed[1], packed[2], packed[3]) : make_uint4(0, 0, 0, 0);
+              *reinterpret_cast<uint4 *>(dst + Cfg::a_lbo) = live[m] ? make_uint4(packed[4], packed[5], packed[6], packed[7]) : make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_a + 8 * s);
+      }
     }
-  } else if (warp == 8) {
-    // ---------------- TMA: X tile [BN tokens x 128 columns] per stage ----------------
+  } else if (warp == kTmaWarp) {
+    // ---------------- TMA: staged X tile [BN tokens x BK columns] per stage ----------------
     if (lane == 0) {
       int issued = 0;
       for (int kt = 0; kt < KT; ++kt) {
         const int s = kt % S;
         if (kt >= S && !mbar_wait(empty + 8 * s, ((kt / S) - 1) & 1, abort_flag, p.status, 2)) break;
         mbar_expect_tx(full_b + 8 * s, Cfg::b_stage);
-        tma_load_3d(b_s + s * Cfg::b_stage, &x_map, full_b + 8 * s, 0, tok0, kt * kChunks);
+        tma_load_3d(b_s + s * Cfg::b_stage, &x_map, full_b + 8 * s, 0, tok0 / 32, kt * Cfg::chunks);
         issued = kt + 1;
       }
       if (*abort_flag) {
@@ -237,7 +321,7 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
     // ---------------- MMA issue ----------------
     if (lane == 0) {
       // D = f32 (bits 4-5 = 1), A = B = f16 (format 0), both K-major, N at bit 17, M at bit 24
-      const unsigned idesc = (1u << 4) | (unsigned(BN >> 3) << 17) | (unsigned(kBM >> 4) << 24);
+      const unsigned idesc = (1u << 4) | (unsigned(BN >> 3) << 17) | (unsigned(kMmaM >> 4) << 24);
       bool ok = true;
       for (int kt = 0; kt < KT && ok; ++kt) {
         const int s = kt % S;
@@ -246,11 +330,13 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < kBK / 16; ++j) {
-          const unsigned long long adesc = smem_desc(a_s + s * kAStage + j * 2 * kALbo, kALbo, kASbo);
-          const unsigned long long bdesc = smem_desc(b_s + s * Cfg::b_stage + j * 2 * Cfg::b_lbo, Cfg::b_lbo, 128);
-          umma_bf16(tmem_base, adesc, bdesc, idesc, (kt | j) ? 1u : 0u);
-        }
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+          for (int j = 0; j < BK / 16; ++j) {
+            const unsigned long long adesc = smem_desc(a_s + s * Cfg::a_stage + m * 16 * kASbo + j * 2 * Cfg::a_lbo, Cfg::a_lbo, kASbo);
+            const unsigned long long bdesc = smem_desc(b_s + s * Cfg::b_stage + j * 2 * Cfg::b_lbo, Cfg::b_lbo, 128);
+            umma_bf16(tmem_base + unsigned(m * BN), adesc, bdesc, idesc, (kt | j) ? 1u : 0u);
+          }
         umma_commit(empty + 8 * s);        // frees the stage when these MMAs have read it
       }
       if (ok) umma_commit(accum);          // accumulators complete
@@ -263,12 +349,14 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ready) {
       const int quarter = warp & 3;
-      const int row = row0 + quarter * 32 + lane;
-      const float bias = (row < p.M && p.bias) ? __bfloat162float(p.bias[row]) : 0.f;
-      const float row_scale = row < p.M ? p.scales[row] : 0.f;
-      for (int c = warp >> 2; c < BN / 32; c += 2) {
+      // the warps of one lane quarter share its MT x (BN/32) accumulator chunks
+      for (int item = warp >> 2; item < MT * (BN / 32); item += kProducerWarps / 4) {
+        const int m = item / (BN / 32), c = item % (BN / 32);
+        const int row = row0 + m * kMmaM + quarter * 32 + lane;
+        const float bias = (row < p.M && p.bias) ? __bfloat162float(p.bias[row]) : 0.f;
+        const float row_scale = row < p.M ? p.scales[row] : 0.f;
         unsigned v[32];
-        tmem_load32(tmem_base + (unsigned(quarter * 32) << 16) + unsigned(c * 32), v);
+        tmem_load32(tmem_base + (unsigned(quarter * 32) << 16) + unsigned(m * BN + c * 32), v);
         if (row < p.M) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -282,9 +370,9 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(unsigned(BN)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(unsigned(Cfg::tmem_columns)) : "memory");
   }
 }
 
@@ -305,24 +393,31 @@ static EncodeTiled encode_tiled_entry() {
   return entry;
 }
 
-// Tile candidates behind the reference's backend ids 5..9 (texelator/autotune.py:16-22): token-tile
-// widths of the tcgen05 kernel; id 9 is the streamed mma.sync path (handled by the dispatcher).
-static int backend_tokens(int backend) {
+// Tile candidates behind the reference's backend ids 5..9 (texelator/autotune.py:16-22):
+//   5: 128 rows x 256 tokens (baseline)   6: 256 x 256   7: 512 x 128   8: 128 x 64   9: 128 x 32
+// Tall tiles re-read the activations less often (tensor-bound prompts); narrow ones suit short prompts
+// where the weight stream is the bound.
+struct TileShape {
+  int mt, bn, bk;
+};
+static TileShape backend_shape(int backend) {
   switch (backend) {
-    case 5: return 256;
-    case 6: return 128;
-    case 7: return 64;
-    case 8: return 32;
-    default: return 0;
+    case 5: return {1, 256, 128};
+    case 6: return {2, 256, 64};
+    case 7: return {4, 128, 64};
+    case 8: return {1, 64, 128};
+    case 9: return {1, 32, 128};
+    default: return {0, 0, 0};
   }
 }
 
 bool prefill_tile_eligible(const Handle *h, int backend, int tokens) {
-  return backend_tokens(backend) != 0 && tokens >= 1 && h->K % 16 == 0 && encode_tiled_entry() != nullptr;
+  return backend_shape(backend).mt != 0 && tokens >= 1 && h->K % 16 == 0 && encode_tiled_entry() != nullptr;
 }
 
-template <int BN>
+template <int MT, int BN, int BK>
 static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream) {
+  using Cfg = TileConfig<MT, BN, BK>;
   Workspace *ws = workspace_for(h->device);
   if (!ws) return TX_ECUDA;
   static std::mutex guard;
@@ -330,28 +425,31 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
   {
     std::lock_guard<std::mutex> lock(guard);
     if (!configured[h->device]) {
-      TX_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(TileConfig<BN>::smem)));
+      TX_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<MT, BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg::smem)));
       configured[h->device] = true;
     }
   }
   // Activations are staged once as fp16 after an exact per-token power-of-two rescale (the decode GEMV's
   // arithmetic), in chunks of tokens that fit the per-device scratch.
   const int KP = h->KI * 128;
-  const int chunk_tokens = int(std::min<size_t>(std::min<size_t>(ws->xprep_halfs / size_t(KP), 65536), size_t(tokens)));
-  if (chunk_tokens < 1) return fail(TX_EINVAL, "K is too large for the prefill activation scratch");
-  for (int t0 = 0; t0 < tokens; t0 += chunk_tokens) {
-    const int n = std::min(chunk_tokens, tokens - t0);
-    int rc = launch_activation_prepass(x + size_t(t0) * h->K, ws->xprep, ws->xmul, n, h->K, KP, stream);
-    if (rc != TX_OK) return rc;
-    // staged X viewed as [KP/8 chunks][n tokens][8 elements]: one box lands as BN-token core-matrix columns
+  const int capacity = int(std::min<size_t>(ws->xprep_halfs / size_t(KP), 65536)) & ~31;   // staged tokens are padded to 32
+  if (capacity < 32) return fail(TX_EINVAL, "K is too large for the prefill activation scratch");
+  for (int t0 = 0; t0 < tokens; t0 += capacity) {
+    const int n = std::min(capacity, tokens - t0);
+    const int padded_tokens = (n + 31) & ~31;
+    stage_activations_kernel<<<padded_tokens / 8, kStageThreads, 0, stream>>>(x + size_t(t0) * h->K, ws->xprep, ws->xmul, h->K, KP, n,
+                                                                    padded_tokens);
+    count_launch();
+    // staged X viewed as [KP/8 chunks][padded_tokens/32][32 tokens x 8 elements]: a box is BN/32 runs of
+    // 512 contiguous bytes per chunk and lands as BN-token core-matrix columns
     CUtensorMap map;
-    cuuint64_t dims[3] = {8, cuuint64_t(n), cuuint64_t(KP / 8)};
-    cuuint64_t strides[2] = {cuuint64_t(KP) * 2, 16};
-    cuuint32_t box[3] = {8, cuuint32_t(BN), cuuint32_t(kChunks)};
+    cuuint64_t dims[3] = {256, cuuint64_t(padded_tokens / 32), cuuint64_t(KP / 8)};
+    cuuint64_t strides[2] = {512, cuuint64_t(padded_tokens) * 16};
+    cuuint32_t box[3] = {256, cuuint32_t(BN / 32), cuuint32_t(Cfg::chunks)};
     cuuint32_t elem[3] = {1, 1, 1};
     CUresult cr = encode_tiled_entry()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, ws->xprep, dims, strides, box, elem,
                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(TX_ECUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(cr)));
     PrefillParams p{};
     p.tiles = reinterpret_cast<const uint4 *>(h->tiles);
@@ -367,8 +465,8 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
     p.MT = h->MT;
     p.T = n;
     p.palette = h->palette;
-    dim3 grid((h->M + kBM - 1) / kBM, (n + BN - 1) / BN);
-    prefill_umma_kernel<BN><<<grid, kPrefillThreads, TileConfig<BN>::smem, stream>>>(p, map);
+    dim3 grid((h->M + Cfg::rows - 1) / Cfg::rows, (n + BN - 1) / BN);
+    prefill_umma_kernel<MT, BN, BK><<<grid, kPrefillThreads, Cfg::smem, stream>>>(p, map);
     count_launch();
   }
   TX_CUDA(cudaGetLastError());
@@ -376,42 +474,44 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
 }
 
 int launch_prefill_tile(const Handle *h, int backend, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream) {
-  if (tokens > 65535 * 32) return fail(TX_EINVAL, "token grid exceeds CUDA grid.y limit");
-  switch (backend_tokens(backend)) {
-    case 256: return launch_tile<256>(h, x, y, tokens, stream);
-    case 128: return launch_tile<128>(h, x, y, tokens, stream);
-    case 64: return launch_tile<64>(h, x, y, tokens, stream);
-    case 32: return launch_tile<32>(h, x, y, tokens, stream);
+  switch (backend) {
+    case 5: return launch_tile<1, 256, 128>(h, x, y, tokens, stream);
+    case 6: return launch_tile<2, 256, 64>(h, x, y, tokens, stream);
+    case 7: return launch_tile<4, 128, 64>(h, x, y, tokens, stream);
+    case 8: return launch_tile<1, 64, 128>(h, x, y, tokens, stream);
+    case 9: return launch_tile<1, 32, 128>(h, x, y, tokens, stream);
     default: return fail(TX_EINVAL, "backend is not a tensor-core tile candidate");
   }
 }
 
-template <int BN>
+template <int MT, int BN, int BK>
 static int tile_info(int64_t out[9]) {
+  using Cfg = TileConfig<MT, BN, BK>;
   cudaFuncAttributes attributes{};
-  TX_CUDA(cudaFuncGetAttributes(&attributes, prefill_umma_kernel<BN>));
-  TX_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(TileConfig<BN>::smem)));
+  TX_CUDA(cudaFuncGetAttributes(&attributes, prefill_umma_kernel<MT, BN, BK>));
+  TX_CUDA(cudaFuncSetAttribute(prefill_umma_kernel<MT, BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg::smem)));
   int active = 0;
-  TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&active, prefill_umma_kernel<BN>, kPrefillThreads, TileConfig<BN>::smem));
+  TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&active, prefill_umma_kernel<MT, BN, BK>, kPrefillThreads, Cfg::smem));
   out[0] = attributes.numRegs;
   out[1] = int64_t(attributes.sharedSizeBytes);
   out[2] = int64_t(attributes.localSizeBytes);
   out[3] = attributes.maxThreadsPerBlock;
-  out[4] = int64_t(TileConfig<BN>::smem);
-  out[5] = kBM;   // output rows per CTA
-  out[6] = BN;    // tokens per CTA
-  out[7] = kBK;   // columns per pipeline stage
+  out[4] = int64_t(Cfg::smem);
+  out[5] = Cfg::rows;   // output rows per CTA
+  out[6] = BN;          // tokens per CTA
+  out[7] = BK;          // columns per pipeline stage
   out[8] = active;
   return TX_OK;
 }
 
 int prefill_kernel_info(int backend, int64_t out[9]) {
-  switch (backend_tokens(backend)) {
-    case 256: return tile_info<256>(out);
-    case 128: return tile_info<128>(out);
-    case 64: return tile_info<64>(out);
-    case 32: return tile_info<32>(out);
-    default: return gemv_kernel_info(out);   // id 9: the streamed mma.sync path
+  switch (backend) {
+    case 5: return tile_info<1, 256, 128>(out);
+    case 6: return tile_info<2, 256, 64>(out);
+    case 7: return tile_info<4, 128, 64>(out);
+    case 8: return tile_info<1, 64, 128>(out);
+    case 9: return tile_info<1, 32, 128>(out);
+    default: return fail(TX_EINVAL, "backend is not a tensor-core tile candidate");
   }
 }
 
