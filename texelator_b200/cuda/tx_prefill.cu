@@ -394,7 +394,7 @@ static EncodeTiled encode_tiled_entry() {
 }
 
 // Tile candidates behind the reference's backend ids 5..9 (texelator/autotune.py:16-22):
-//   5: 128 rows x 256 tokens (baseline)   6: 256 x 256   7: 512 x 128   8: 128 x 64   9: 128 x 32
+//   5: 128 rows x 256 tokens (baseline)   6: 256 x 256   7: 128 x 128   8: 128 x 64   9: 128 x 32
 // Tall tiles re-read the activations less often (tensor-bound prompts); narrow ones suit short prompts
 // where the weight stream is the bound.
 struct TileShape {
@@ -404,7 +404,7 @@ static TileShape backend_shape(int backend) {
   switch (backend) {
     case 5: return {1, 256, 128};
     case 6: return {2, 256, 64};
-    case 7: return {4, 128, 64};
+    case 7: return {1, 128, 128};
     case 8: return {1, 64, 128};
     case 9: return {1, 32, 128};
     default: return {0, 0, 0};
@@ -477,7 +477,7 @@ int launch_prefill_tile(const Handle *h, int backend, const __nv_bfloat16 *x, __
   switch (backend) {
     case 5: return launch_tile<1, 256, 128>(h, x, y, tokens, stream);
     case 6: return launch_tile<2, 256, 64>(h, x, y, tokens, stream);
-    case 7: return launch_tile<4, 128, 64>(h, x, y, tokens, stream);
+    case 7: return launch_tile<1, 128, 128>(h, x, y, tokens, stream);
     case 8: return launch_tile<1, 64, 128>(h, x, y, tokens, stream);
     case 9: return launch_tile<1, 32, 128>(h, x, y, tokens, stream);
     default: return fail(TX_EINVAL, "backend is not a tensor-core tile candidate");
@@ -508,7 +508,7 @@ int prefill_kernel_info(int backend, int64_t out[9]) {
   switch (backend) {
     case 5: return tile_info<1, 256, 128>(out);
     case 6: return tile_info<2, 256, 64>(out);
-    case 7: return tile_info<4, 128, 64>(out);
+    case 7: return tile_info<1, 128, 128>(out);
     case 8: return tile_info<1, 64, 128>(out);
     case 9: return tile_info<1, 32, 128>(out);
     default: return fail(TX_EINVAL, "backend is not a tensor-core tile candidate");
