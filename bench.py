@@ -359,7 +359,7 @@ def main() -> None:
     parser.add_argument("--model", default="27b-class")
     parser.add_argument("--prompt", type=int, default=2048)
     parser.add_argument("--decode", type=int, default=512)
-    parser.add_argument("--lookahead", type=int, default=2)
+    parser.add_argument("--lookahead", type=int, default=4)
     parser.add_argument("--layers", type=int, default=0, help="override the layer count (profiling aid; not a bench result)")
     parser.add_argument("--micro", default=None, help="MxK[xT]: time one linear shape alone (profiling aid)")
     parser.add_argument("--backend", type=int, default=5, help="prefill backend id for --micro with T >= 16")

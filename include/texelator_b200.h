@@ -87,6 +87,19 @@ int tx_linear(uint64_t handle, const void *x, void *y, int tokens, int dtype, vo
  * stream capture.  Every call on a device uses the same array: calls that overlap on the GPU race. */
 int tx_linear_static_scratch(uint64_t handle, const void *x, void *y, int tokens, int dtype, void *stream);
 
+/* No counterpart in the reference (its decode loop leaves these steps to PyTorch kernels between the
+ * linears, texelator/cli.py:189-219).  Decode linear with its neighbours fused into the same launch:
+ *   norm_weight != NULL : r = bf16(x + delta) (delta may be NULL), a = bf16(rmsnorm(r, eps) * norm_weight)
+ *                         feeds the linear; r is also stored to residual_out when that is non-NULL
+ *                         (it must not alias x).  K <= 18432.
+ *   swiglu != 0         : the handle's rows are (gate, up) pairs -- in every group of 16 rows, rows 0-7
+ *                         are gate rows and rows 8-15 the matching up rows -- and
+ *                         y[t, 8*g + i] = silu(lin[16*g + i]) * lin[16*g + 8 + i]; y is [tokens, M/2].
+ * Rounding points are those of the separate steps (bf16 after the add, after the norm, after each
+ * linear output, after the product).  At most 2 tokens with tokens * K <= 36864; TX_DECODE_ALU_MMA only. */
+int tx_linear_fused(uint64_t handle, const void *x, const void *delta, const void *norm_weight, float eps, void *residual_out,
+                    int swiglu, void *y, int tokens, int dtype, void *stream);
+
 /* set_lookahead: texelator_cuda.cu:1471-1478.  k in {1,2,3,4,6,8}: 1 KiB weight requests each
  * warp keeps in flight (the reference: texture requests in flight). */
 int tx_set_lookahead(uint64_t handle, int lookahead);
@@ -150,12 +163,18 @@ int tx_kernel_status(int device, int clear);
  *                      caches [kv_heads, max_len, head_dim] at *position (device int64)
  *   attention_decode : one query per head over cache positions 0..*position, grouped-query; `scratch`
  *                      holds q_heads * ceil(max_len/128) * (head_dim+2) floats; head_dim must be 128
+ *   attention_step   : rope_append + attention_decode of one token in ONE launch (q is rotated on the
+ *                      fly, qkv is left untouched); `scratch` holds q_heads * ceil(max_len/64) * 132
+ *                      floats; head_dim 128, at most 16384 positions
  *   silu_mul         : out[t,i] = silu(gate_up[t,i]) * gate_up[t,intermediate+i]                     */
 int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, int tokens, int hidden, float eps, void *stream);
 int tx_aux_rope_append(void *qkv, const float *cos_table, const float *sin_table, const void *position, void *k_cache,
                        void *v_cache, int q_heads, int kv_heads, int head_dim, int max_len, void *stream);
 int tx_aux_attention_decode(const void *qkv, const void *k_cache, const void *v_cache, const void *position, float *scratch,
                             void *out, int q_heads, int kv_heads, int head_dim, int max_len, float scale, void *stream);
+int tx_aux_attention_step(const void *qkv, const float *cos_table, const float *sin_table, const void *position, void *k_cache,
+                          void *v_cache, float *scratch, void *out, int q_heads, int kv_heads, int head_dim, int max_len,
+                          float scale, void *stream);
 int tx_aux_silu_mul(const void *gate_up, void *out, int tokens, int intermediate, void *stream);
 
 /* Number of this library's kernels launched by the calling process since load (all threads). */

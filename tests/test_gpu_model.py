@@ -72,11 +72,14 @@ def test_fused_decode_step_matches_pytorch_glue():
             model.decode_eager(fused=True)
             assert _cosine(model.last_hidden, hidden[step]) >= 0.9995, step
         model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
-        model.capture()
-        assert model.launches_per_step == model.config.layers * 10 + 1
-        for step in range(3):      # graph replays overlap kernels (programmatic dependent launch): same results
-            model.decode_graph()
-            torch.cuda.synchronize()
-            assert _cosine(model.last_hidden, hidden[step]) >= 0.9995, step
+        for fuse_norm, per_layer in ((False, 7), (True, 5)):
+            model.fuse_norm = fuse_norm
+            model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
+            model.capture()
+            assert model.launches_per_step == model.config.layers * per_layer + 1
+            for step in range(3):      # graph replays overlap kernels (programmatic dependent launch): same results
+                model.decode_graph()
+                torch.cuda.synchronize()
+                assert _cosine(model.last_hidden, hidden[step]) >= 0.9995, (fuse_norm, step)
     finally:
         model.free()

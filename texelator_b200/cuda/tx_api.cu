@@ -218,6 +218,26 @@ int tx_linear_static_scratch(uint64_t handle, const void *x, void *y, int tokens
   return rc;
 }
 
+int tx_linear_fused(uint64_t handle, const void *x, const void *delta, const void *norm_weight, float eps, void *residual_out,
+                    int swiglu, void *y, int tokens, int dtype, void *stream_ptr) {
+  Handle *h = as_handle(handle);
+  if (!h) return fail(TX_EINVAL, "null Texelator handle");
+  if (!x || !y || dtype != TX_DTYPE_BF16) return fail(TX_EINVAL, "input must be contiguous CUDA BF16");
+  if (tokens < 1) return fail(TX_EINVAL, "tokens must be positive");
+  if (h->decode_path != TX_DECODE_ALU_MMA) return fail(TX_EUNSUPPORTED, "fused linear runs on the ALU mma decode path only");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(delta) |
+       reinterpret_cast<uintptr_t>(norm_weight) | reinterpret_cast<uintptr_t>(residual_out)) & 15)
+    return fail(TX_EINVAL, "activation, norm and output pointers must be 16-byte aligned");
+  int current = 0;
+  TX_CUDA(cudaGetDevice(&current));
+  if (current != h->device) TX_CUDA(cudaSetDevice(h->device));
+  int rc = launch_gemv_fused(h, static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(delta),
+                             static_cast<const __nv_bfloat16 *>(norm_weight), eps, static_cast<__nv_bfloat16 *>(residual_out),
+                             swiglu != 0, static_cast<__nv_bfloat16 *>(y), tokens, static_cast<cudaStream_t>(stream_ptr));
+  if (current != h->device) cudaSetDevice(current);
+  return rc;
+}
+
 int tx_set_lookahead(uint64_t handle, int lookahead) {
   Handle *h = as_handle(handle);
   if (!h) return fail(TX_EINVAL, "null Texelator handle");

@@ -191,6 +191,8 @@ int launch_retile(const uint8_t *rowmajor_dev, Handle *h, cudaStream_t stream);
 int launch_untile(const Handle *h, uint8_t *rowmajor_dev, cudaStream_t stream);
 int launch_dequant(const Handle *h, void *out, int what, cudaStream_t stream);
 int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
+int launch_gemv_fused(const Handle *h, const __nv_bfloat16 *x, const __nv_bfloat16 *delta, const __nv_bfloat16 *gamma, float eps,
+                      __nv_bfloat16 *residual_out, bool swiglu, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_gemv_exact(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_gemv_texture(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);

@@ -50,7 +50,15 @@ struct GemvParams {
   int M, K, KI, T, MT;
   int KP;                   // KI * 128
   int palette;              // TX_PALETTE_*
+  // fused prologue (FUSE & 1): x is the residual stream; a = rmsnorm(bf16(x + delta)) * gamma feeds the linear
+  const __nv_bfloat16 *delta;   // [T, K] or null
+  const __nv_bfloat16 *gamma;   // [K]
+  __nv_bfloat16 *residual_out;  // [T, K] or null: receives bf16(x + delta); must not alias x
+  float eps;
 };
+
+constexpr int kFuseNorm = 1;     // residual add + RMSNorm in the activation staging
+constexpr int kFuseSwiglu = 2;   // rows are (gate, up) pairs: y[t, i] = silu(gate_i) * up_i
 
 // Pre-pass for larger token counts: one CTA per token writes scaled fp16 activations and the
 // per-token multiplier 2^s/889 to scratch.
@@ -84,9 +92,10 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const __nv_bfl
 // combine their fp32 partial tiles through shared memory (double-buffered, one named barrier per
 // tile).  No global scratch, no atomics, deterministic summation order.
 // ------------------------------------------------------------------------------------------
-template <int LOOKAHEAD, int NT, bool PRE, bool LOWMODE>
+template <int LOOKAHEAD, int NT, bool PRE, bool LOWMODE, int FUSE = 0>
 __global__ void __launch_bounds__(kGemvThreads, (NT == 1 && LOOKAHEAD <= 2) ? 3 : (NT <= 2 ? 2 : 1))
 gemv_tile_kernel(const GemvParams p) {
+  static_assert(FUSE == 0 || (NT == 1 && !PRE), "fused variants stage their activations in the CTA");
   extern __shared__ uint8_t smem_raw[];
   const unsigned sbase = unsigned(__cvta_generic_to_shared(smem_raw));
   const unsigned lut_s = (sbase + kLutBytes - 1) & ~unsigned(kLutBytes - 1);
@@ -158,15 +167,75 @@ gemv_tile_kernel(const GemvParams p) {
       const uint4 *xp = reinterpret_cast<const uint4 *>(p.x + size_t(tok) * p.K);
       uint4 held[kXChunks];
       unsigned m = 0;
+      if (FUSE & kFuseNorm) {
+        // residual add and RMSNorm with the rounding points of separate kernels: r = bf16(x + delta),
+        // a = bf16(r * inv * gamma).  Every CTA computes the row (K <= 18432 stays in registers); CTA 0
+        // also stores r.  Rows longer than that are rejected by the launcher.
+        const uint4 *dp = p.delta ? reinterpret_cast<const uint4 *>(p.delta + size_t(tok) * p.K) : nullptr;
+        uint4 *rp = (p.residual_out && blockIdx.x == 0) ? reinterpret_cast<uint4 *>(p.residual_out + size_t(tok) * p.K) : nullptr;
+        float ss = 0.f;
 #pragma unroll
-      for (int c = 0; c < kXChunks; ++c) {
-        const int i = tid + c * kGemvThreads;
-        if (i < chunks) {
-          held[c] = __ldcg(xp + i);   // L2 read: another kernel wrote these moments ago
-          m = max(m, chunk_absmax(held[c]));
+        for (int c = 0; c < kXChunks; ++c) {
+          const int i = tid + c * kGemvThreads;
+          if (i < chunks) {
+            uint4 v = __ldcg(xp + i);
+            __nv_bfloat162 *pv = reinterpret_cast<__nv_bfloat162 *>(&v);
+            if (dp) {
+              const uint4 d = __ldcg(dp + i);
+              const __nv_bfloat162 *pd = reinterpret_cast<const __nv_bfloat162 *>(&d);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(pv[e]), b = __bfloat1622float2(pd[e]);
+                pv[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+              }
+            }
+            if (rp) rp[i] = v;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 a = __bfloat1622float2(pv[e]);
+              ss += a.x * a.x + a.y * a.y;
+            }
+            held[c] = v;
+          }
         }
+#pragma unroll
+        for (int d = 16; d; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+        float *ss_part = reinterpret_cast<float *>(red + kGemvWarps);
+        if (lane == 0) ss_part[warp] = ss;
+        __syncthreads();
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < kGemvWarps; ++w) total += ss_part[w];
+        const float inv = rsqrtf(total / float(p.K) + p.eps);
+        const uint4 *gp = reinterpret_cast<const uint4 *>(p.gamma);
+#pragma unroll
+        for (int c = 0; c < kXChunks; ++c) {
+          const int i = tid + c * kGemvThreads;
+          if (i < chunks) {
+            uint4 v = held[c];
+            const uint4 gw = gp[i];
+            __nv_bfloat162 *pv = reinterpret_cast<__nv_bfloat162 *>(&v);
+            const __nv_bfloat162 *pg = reinterpret_cast<const __nv_bfloat162 *>(&gw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 a = __bfloat1622float2(pv[e]), gm = __bfloat1622float2(pg[e]);
+              pv[e] = __floats2bfloat162_rn(a.x * inv * gm.x, a.y * inv * gm.y);
+            }
+            held[c] = v;
+            m = max(m, chunk_absmax(v));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kXChunks; ++c) {
+          const int i = tid + c * kGemvThreads;
+          if (i < chunks) {
+            held[c] = __ldcg(xp + i);   // L2 read: another kernel wrote these moments ago
+            m = max(m, chunk_absmax(held[c]));
+          }
+        }
+        for (int i = tid + kXChunks * kGemvThreads; i < chunks; i += kGemvThreads) m = max(m, chunk_absmax(__ldcg(xp + i)));
       }
-      for (int i = tid + kXChunks * kGemvThreads; i < chunks; i += kGemvThreads) m = max(m, chunk_absmax(__ldcg(xp + i)));
       m = __reduce_max_sync(0xffffffffu, m);
       if (lane == 0) red[warp] = m;
       __syncthreads();
@@ -206,6 +275,8 @@ gemv_tile_kernel(const GemvParams p) {
   constexpr int kElems = NT * 128;
   constexpr int kPerThread = (kElems + 31) / 32;   // upper bound (one worker warp)
   float row_scale[kPerThread], row_bias[kPerThread];
+  constexpr int kPairConstants = (FUSE & kFuseSwiglu) ? kPerThread : 1;
+  float up_scale[kPairConstants], up_bias[kPairConstants];   // SwiGLU: constants of the paired up row (tile row + 8)
   bool row_live[kPerThread];   // this thread's element exists (row < M, token < T)
   auto load_row_constants = [&](int rt) {
 #pragma unroll
@@ -214,9 +285,14 @@ gemv_tile_kernel(const GemvParams p) {
       int row = rt * 16 + ((e >> 6) & 1) * 8 + ((e & 31) >> 2);
       int tok = (e >> 7) * 8 + 2 * (e & 3) + ((e >> 5) & 1);
       bool ok = e < kElems && row < p.M && tok < p.T;
+      if (FUSE & kFuseSwiglu) ok = ok && ((e >> 6) & 1) == 0;   // the gate element's thread finishes the pair
       row_live[j] = ok;
       row_scale[j] = ok ? p.scales[row] : 0.f;
       row_bias[j] = ok && p.bias ? __bfloat162float(p.bias[row]) : 0.f;
+      if (FUSE & kFuseSwiglu) {
+        up_scale[j] = ok ? p.scales[row + 8] : 0.f;
+        up_bias[j] = ok && p.bias ? __bfloat162float(p.bias[row + 8]) : 0.f;
+      }
     }
   };
 
@@ -281,7 +357,17 @@ gemv_tile_kernel(const GemvParams p) {
             const int c = e >> 5, ln = e & 31;
             const int row = tile * 16 + ((c >> 1) & 1) * 8 + (ln >> 2);
             const int tok = (c >> 2) * 8 + 2 * (ln & 3) + (c & 1);
-            p.y[size_t(tok) * p.M + row] = __float2bfloat16(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j]));
+            if (FUSE & kFuseSwiglu) {
+              // element e + 64 is the up row of this gate row; both are rounded to bf16 first, like the
+              // outputs of an unfused linear, then combined with silu_mul's arithmetic
+              float up_sum = 0.f;
+              for (int w = 0; w < WS; ++w) up_sum += src[w * kElems + 64];
+              const float gate = __bfloat162float(__float2bfloat16(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j])));
+              const float up = __bfloat162float(__float2bfloat16(fmaf(up_sum, up_scale[j] * tokmul[tok], up_bias[j])));
+              p.y[size_t(tok) * (p.M / 2) + tile * 8 + (ln >> 2)] = __float2bfloat16(gate / (1.f + __expf(-gate)) * up);
+            } else {
+              p.y[size_t(tok) * p.M + row] = __float2bfloat16(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j]));
+            }
           }
         }
         buf ^= 1;
@@ -414,8 +500,28 @@ static GemvKernel pick_tokens(int lookahead, int nt, bool pre) {
   }
 }
 
-static GemvKernel pick_kernel(int lookahead, int nt, bool pre, bool low_mode) {
-  return low_mode ? pick_tokens<true>(lookahead, nt, pre) : pick_tokens<false>(lookahead, nt, pre);
+template <bool LOWMODE, int FUSE>
+static GemvKernel pick_fused_lookahead(int lookahead) {
+  switch (lookahead) {
+    case 1: return gemv_tile_kernel<1, 1, false, LOWMODE, FUSE>;
+    case 2: return gemv_tile_kernel<2, 1, false, LOWMODE, FUSE>;
+    case 3: return gemv_tile_kernel<3, 1, false, LOWMODE, FUSE>;
+    case 4: return gemv_tile_kernel<4, 1, false, LOWMODE, FUSE>;
+    case 6: return gemv_tile_kernel<6, 1, false, LOWMODE, FUSE>;
+    default: return gemv_tile_kernel<8, 1, false, LOWMODE, FUSE>;
+  }
+}
+
+// fuse: kFuseNorm, kFuseSwiglu or both; fused variants exist for in-CTA staging (one token tile) only
+static GemvKernel pick_kernel(int lookahead, int nt, bool pre, bool low_mode, int fuse = 0) {
+  switch (fuse) {
+    case 0: return low_mode ? pick_tokens<true>(lookahead, nt, pre) : pick_tokens<false>(lookahead, nt, pre);
+    case kFuseNorm: return low_mode ? pick_fused_lookahead<true, kFuseNorm>(lookahead) : pick_fused_lookahead<false, kFuseNorm>(lookahead);
+    case kFuseSwiglu: return low_mode ? pick_fused_lookahead<true, kFuseSwiglu>(lookahead) : pick_fused_lookahead<false, kFuseSwiglu>(lookahead);
+    default:
+      return low_mode ? pick_fused_lookahead<true, kFuseNorm | kFuseSwiglu>(lookahead)
+                      : pick_fused_lookahead<false, kFuseNorm | kFuseSwiglu>(lookahead);
+  }
 }
 
 static size_t gemv_smem_bytes(int KP, int tokens, int nt) {
@@ -441,14 +547,15 @@ struct GemvPlan {
   size_t smem;
 };
 
-static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan) {
+static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0) {
   Workspace *ws = workspace_for(h->device);
   if (!ws) return TX_ECUDA;
   int KP = h->KI * 128;
   plan.nt = token_tiles(tokens);
   // in-CTA activation conversion only while it stays a short prologue
   plan.pre = !(tokens <= 2 && size_t(tokens) * h->K <= 36864);
-  plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre, h->has_low_mode);
+  if (fuse && plan.pre) return fail(TX_EINVAL, "fused linear handles at most 2 tokens with tokens * K <= 36864");
+  plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre, h->has_low_mode, fuse);
   plan.smem = gemv_smem_bytes(KP, tokens, plan.nt);
   // attribute + occupancy queries are cached per (device, kernel, shared bytes)
   static std::mutex guard;
@@ -508,6 +615,43 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
     TX_CUDA(launch_pdl(plan.kernel, dim3(plan.grid), dim3(kGemvThreads), plan.smem, stream, p));
     count_launch();
   }
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
+// Decode linear with fused neighbours: optional residual add + RMSNorm in front (the activation
+// staging every CTA does anyway), optional SwiGLU behind (rows packed as gate/up pairs).
+int launch_gemv_fused(const Handle *h, const __nv_bfloat16 *x, const __nv_bfloat16 *delta, const __nv_bfloat16 *gamma, float eps,
+                      __nv_bfloat16 *residual_out, bool swiglu, __nv_bfloat16 *y, int tokens, cudaStream_t stream) {
+  const int fuse = (gamma ? kFuseNorm : 0) | (swiglu ? kFuseSwiglu : 0);
+  if (!gamma && (delta || residual_out)) return fail(TX_EINVAL, "delta and residual_out need a norm weight");
+  if (gamma && h->K > kXChunks * kGemvThreads * 8) return fail(TX_EINVAL, "fused RMSNorm handles K up to 18432");
+  if (residual_out && residual_out == x) return fail(TX_EINVAL, "residual_out must not alias x");
+  if (swiglu && h->M % 16) return fail(TX_EINVAL, "SwiGLU pairs need M to be a multiple of 16");
+  if (fuse == 0) return launch_gemv(h, x, y, tokens, stream);
+  GemvPlan plan;
+  int rc = plan_gemv(h, tokens, plan, fuse);
+  if (rc != TX_OK) return rc;
+  GemvParams p{};
+  p.tiles = reinterpret_cast<const uint4 *>(h->tiles);
+  p.flags = h->unit_flags;
+  p.scales = h->scales;
+  p.bias = h->bias;
+  p.x = x;
+  p.y = y;
+  p.M = h->M;
+  p.K = h->K;
+  p.KI = h->KI;
+  p.MT = h->MT;
+  p.T = tokens;
+  p.KP = h->KI * 128;
+  p.palette = h->palette;
+  p.delta = delta;
+  p.gamma = gamma;
+  p.residual_out = residual_out;
+  p.eps = eps;
+  TX_CUDA(launch_pdl(plan.kernel, dim3(plan.grid), dim3(kGemvThreads), plan.smem, stream, p));
+  count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;
 }

@@ -65,6 +65,15 @@ CONFIGS = {
 }
 
 
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Rows of a fused gate/up projection in the pair order of ``tx_linear_fused``'s SwiGLU: every group of
+    16 rows holds 8 gate rows followed by the 8 up rows of the same output columns."""
+    rows = gate.shape[0]
+    if rows % 8 or up.shape != gate.shape:
+        raise ValueError("gate and up must have the same shape with a multiple of 8 rows")
+    return torch.stack([gate.reshape(rows // 8, 8, -1), up.reshape(rows // 8, 8, -1)], 1).reshape(2 * rows, -1)
+
+
 def input_device(model) -> torch.device:
     embedding = model.get_input_embeddings()
     device = getattr(embedding, "output_device", embedding.weight.device)
@@ -146,7 +155,7 @@ class BC4Decoder:
     """
 
     def __init__(self, config: DecoderConfig, device, max_len: int, seed: int = 0, tp_rank: int = 0,
-                 tp_world: int = 1, group=None, lookahead: int = 2, keep_dense: bool = False,
+                 tp_world: int = 1, group=None, lookahead: int = 4, keep_dense: bool = False,
                  weight_std: float = 0.02, prefill_backend: int = 5):
         self.config, self.device, self.max_len = config, torch.device(device), max_len
         self.rank, self.world, self.group = tp_rank, tp_world, group
@@ -180,7 +189,7 @@ class BC4Decoder:
                 del wqkv
                 self.h_o.append(self._pack_columns(randn(c.hidden, c.q_rows), lut))
                 wg, wu = randn(c.intermediate, c.hidden), randn(c.intermediate, c.hidden)
-                wgu = torch.cat([rows_of(wg, self.i_loc), rows_of(wu, self.i_loc)])
+                wgu = interleave_gate_up(rows_of(wg, self.i_loc), rows_of(wu, self.i_loc))
                 del wg, wu
                 self.h_gu.append(self._pack_rows(wgu, lut, None))
                 del wgu
@@ -207,6 +216,7 @@ class BC4Decoder:
             q_heads = c.q_heads // tp_world
             bf = dict(dtype=torch.bfloat16, device=self.device)
             self.buf_h = torch.zeros(1, c.hidden, **bf)
+            self.buf_h2 = torch.zeros(1, c.hidden, **bf)
             self.buf_x = torch.zeros(1, c.hidden, **bf)
             self.buf_qkv = torch.zeros(1, self.q_loc + 2 * self.kv_loc, **bf)
             self.buf_attn = torch.zeros(1, self.q_loc, **bf)
@@ -214,9 +224,13 @@ class BC4Decoder:
             self.buf_gu = torch.zeros(1, 2 * self.i_loc, **bf)
             self.buf_act = torch.zeros(1, self.i_loc, **bf)
             self.buf_down = torch.zeros(1, c.hidden, **bf)
-            self.attn_scratch = torch.zeros(q_heads * ((max_len + 127) // 128) * (c.head_dim + 2), dtype=torch.float32,
-                                            device=self.device)
-            self.fused = c.head_dim == 128 and (c.q_heads // c.kv_heads) <= 8
+            self.attn_scratch = torch.zeros(max(q_heads * ((max_len + 127) // 128) * (c.head_dim + 2),
+                                                self.ext.attention_step_scratch_floats(q_heads, max_len)),
+                                            dtype=torch.float32, device=self.device)
+            self.fused = c.head_dim == 128 and (c.q_heads // c.kv_heads) <= 8 and c.hidden <= 18432 and self.i_loc % 8 == 0
+        # residual add + RMSNorm inside the qkv and gate/up linears instead of separate launches: every CTA
+        # of the linear then repeats the norm, which measured slower than the two small kernels on a B200
+        self.fuse_norm = False
         self.graph = None
         self.launches_per_step = 0
 
@@ -269,8 +283,8 @@ class BC4Decoder:
         out = out.squeeze(0).transpose(0, 1).reshape(tokens, self.q_loc).contiguous()
         h = h + self._reduce(self._linear(self.h_o[layer], out, dense))
         x = _rmsnorm(h, self.norm2[layer], c.rms_eps)
-        gu = self._linear(self.h_gu[layer], x, dense)
-        act = (F.silu(gu[:, :self.i_loc].float()) * gu[:, self.i_loc:].float()).to(h.dtype)
+        gu = self._linear(self.h_gu[layer], x, dense).view(tokens, self.i_loc // 8, 2, 8)     # (gate, up) row pairs
+        act = (F.silu(gu[:, :, 0].float()) * gu[:, :, 1].float()).to(h.dtype).reshape(tokens, self.i_loc)
         return h + self._reduce(self._linear(self.h_down[layer], act, dense))
 
     @torch.no_grad()
@@ -313,26 +327,40 @@ class BC4Decoder:
         self.pos.add_(1)
 
     def _decode_step_fused(self):
-        """One decode step with the library's glue kernels: per layer 4 BC4 GEMVs + 6 small launches."""
+        """One decode step with the library's fused kernels, five launches per layer: qkv linear (with the
+        residual add and RMSNorm in its activation staging), attention step (RoPE, cache append, attention,
+        split merge), o linear, gate/up linear (add + norm in front, SwiGLU behind), down linear."""
         c, ext = self.config, self.ext
         q_heads, kv_heads = c.q_heads // self.world, c.kv_heads // self.world
         torch.index_select(self.embed, 0, self.tok, out=self.buf_h)
+        residual, spare = self.buf_h, self.buf_h2       # the fused linears write x + delta to the other buffer
         delta = None
         for layer in range(c.layers):
-            ext.add_rmsnorm(self.buf_h, delta, self.norm1[layer], self.buf_x, c.rms_eps)
-            ext.linear_out(self.h_qkv[layer], self.buf_x, self.buf_qkv)
-            ext.rope_append(self.buf_qkv, self.cos, self.sin, self.pos, self.k_cache[layer], self.v_cache[layer],
-                            q_heads, kv_heads, c.head_dim)
-            ext.attention_decode(self.buf_qkv, self.k_cache[layer], self.v_cache[layer], self.pos, self.attn_scratch,
-                                 self.buf_attn, q_heads, kv_heads, c.head_dim)
+            if not self.fuse_norm:
+                ext.add_rmsnorm(residual, delta, self.norm1[layer], self.buf_x, c.rms_eps)
+                ext.linear_out(self.h_qkv[layer], self.buf_x, self.buf_qkv)
+            elif delta is None:
+                ext.linear_fused_out(self.h_qkv[layer], residual, self.buf_qkv, norm_weight=self.norm1[layer], eps=c.rms_eps)
+            else:
+                ext.linear_fused_out(self.h_qkv[layer], residual, self.buf_qkv, norm_weight=self.norm1[layer], delta=delta,
+                                     eps=c.rms_eps, residual_out=spare)
+                residual, spare = spare, residual
+            ext.attention_step(self.buf_qkv, self.cos, self.sin, self.pos, self.k_cache[layer], self.v_cache[layer],
+                               self.attn_scratch, self.buf_attn, q_heads, kv_heads, c.head_dim)
             ext.linear_out(self.h_o[layer], self.buf_attn, self.buf_o)
             self._reduce(self.buf_o)
-            ext.add_rmsnorm(self.buf_h, self.buf_o, self.norm2[layer], self.buf_x, c.rms_eps)
-            ext.linear_out(self.h_gu[layer], self.buf_x, self.buf_gu)
-            ext.silu_mul(self.buf_gu, self.buf_act)
+            if self.fuse_norm:
+                ext.linear_fused_out(self.h_gu[layer], residual, self.buf_act, norm_weight=self.norm2[layer], delta=self.buf_o,
+                                     eps=c.rms_eps, residual_out=spare, swiglu=True)
+                residual, spare = spare, residual
+            else:
+                ext.add_rmsnorm(residual, self.buf_o, self.norm2[layer], self.buf_x, c.rms_eps)
+                ext.linear_fused_out(self.h_gu[layer], self.buf_x, self.buf_act, swiglu=True)
             ext.linear_out(self.h_down[layer], self.buf_act, self.buf_down)
             self._reduce(self.buf_down)
             delta = self.buf_down
+        if residual is not self.buf_h:
+            self.buf_h.copy_(residual)
         ext.add_rmsnorm(self.buf_h, delta, self.final_norm, self.buf_x, c.rms_eps)
         self.last_hidden.copy_(self.buf_x)
         logits = self.buf_x @ self.lm_head.T

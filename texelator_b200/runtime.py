@@ -48,6 +48,7 @@ C_API = {
                                      ctypes.POINTER(_u64)]),
     "tx_linear": (_i32, [_u64, _vp, _vp, _i32, _i32, _vp]),
     "tx_linear_static_scratch": (_i32, [_u64, _vp, _vp, _i32, _i32, _vp]),
+    "tx_linear_fused": (_i32, [_u64, _vp, _vp, _vp, ctypes.c_float, _vp, _i32, _vp, _i32, _i32, _vp]),
     "tx_set_lookahead": (_i32, [_u64, _i32]),
     "tx_set_prefill": (_i32, [_u64, _i32, _i32]),
     "tx_set_prefill_backend": (_i32, [_u64, _i32]),
@@ -65,6 +66,7 @@ C_API = {
     "tx_aux_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, ctypes.c_float, _vp]),
     "tx_aux_rope_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "tx_aux_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp]),
+    "tx_aux_attention_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp]),
     "tx_aux_silu_mul": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "tx_launch_count": (ctypes.c_int64, []),
 }
@@ -205,6 +207,25 @@ class _Extension:
         self._check(self._lib.tx_linear_static_scratch(handle, x.data_ptr(), y.data_ptr(), x.numel() // k, DTYPE_BF16, stream))
         return y
 
+    def linear_fused_out(self, handle: int, x: torch.Tensor, y: torch.Tensor, *, norm_weight: torch.Tensor | None = None,
+                         delta: torch.Tensor | None = None, eps: float = 1e-6, residual_out: torch.Tensor | None = None,
+                         swiglu: bool = False) -> None:
+        """Decode linear with fused neighbours, written into ``y``: with ``norm_weight`` the input is the
+        residual stream (``x + delta`` is rounded to bf16, stored to ``residual_out`` and RMS-normalised
+        first); with ``swiglu`` the handle's rows are (gate, up) pairs (``interleave_gate_up`` order) and
+        ``y`` is ``[tokens, M/2]``.  At most two tokens."""
+        m, k, device = self._shapes[handle]
+        tokens = x.numel() // k
+        for tensor in (x, y, norm_weight, delta, residual_out):
+            if tensor is not None and (not tensor.is_cuda or tensor.dtype != torch.bfloat16 or not tensor.is_contiguous()):
+                raise RuntimeError("fused linear tensors must be contiguous CUDA BF16")
+        if y.numel() != tokens * (m // 2 if swiglu else m):
+            raise RuntimeError("output has the wrong size for this handle")
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        self._check(self._lib.tx_linear_fused(handle, x.data_ptr(), ptr(delta), ptr(norm_weight), float(eps), ptr(residual_out),
+                                              int(swiglu), y.data_ptr(), tokens, DTYPE_BF16,
+                                              torch.cuda.current_stream(device).cuda_stream))
+
     def set_lookahead(self, handle: int, lookahead: int) -> None:
         self._check(self._lib.tx_set_lookahead(handle, int(lookahead)))
 
@@ -313,6 +334,21 @@ class _Extension:
         self._check(self._lib.tx_aux_attention_decode(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), position.data_ptr(),
                                                       scratch.data_ptr(), out.data_ptr(), q_heads, kv_heads, head_dim,
                                                       k_cache.shape[1], float(head_dim) ** -0.5, self._stream(qkv)))
+
+    @staticmethod
+    def attention_step_scratch_floats(q_heads: int, max_len: int) -> int:
+        """Size of the fp32 scratch ``attention_step`` needs for caches of ``max_len`` positions."""
+        return q_heads * ((max_len + 63) // 64) * 132
+
+    def attention_step(self, qkv, cos, sin, position, k_cache, v_cache, scratch, out, q_heads: int, kv_heads: int,
+                       head_dim: int) -> None:
+        """RoPE + cache append + single-query attention + split merge of one token in one launch."""
+        if scratch.numel() < self.attention_step_scratch_floats(q_heads, k_cache.shape[1]):
+            raise ValueError("attention_step scratch is too small for this cache length")
+        self._check(self._lib.tx_aux_attention_step(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), position.data_ptr(),
+                                                    k_cache.data_ptr(), v_cache.data_ptr(), scratch.data_ptr(), out.data_ptr(),
+                                                    q_heads, kv_heads, head_dim, k_cache.shape[1], float(head_dim) ** -0.5,
+                                                    self._stream(qkv)))
 
     def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
         tokens, two_i = gate_up.shape
