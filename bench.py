@@ -276,6 +276,7 @@ def run_gpu_arm(args, config) -> None:
     ids = torch.randint(0, config.vocab, (prompt,), generator=torch.Generator().manual_seed(0))
     model.prefill(ids)
     model.tok.fill_(int(ids[-1]))
+    fused_allreduce = world > 1 and not args.nccl_allreduce and model.enable_peer_exchange()
     model.capture()
     steps, warmup = args.steps, max(args.warmup, 3)
 
@@ -294,7 +295,9 @@ def run_gpu_arm(args, config) -> None:
                        "intermediate": config.intermediate, "parallelism": f"tp{world}",
                        "bc4_bytes_per_token": config.bc4_bytes_per_token(),
                        "l2": "per-token weight stream (>=1.3 GB per GPU) is larger than L2; no flush needed",
-                       "lookahead": args.lookahead},
+                       "lookahead": args.lookahead,
+                       "allreduce": ("none" if world == 1 else
+                                     "fused into the norm kernel over NVLink peer memory" if fused_allreduce else "nccl")},
             "e2e": {"value": 1000.0 / ms_e2e, "unit": UNIT, "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
             "gpu_launches": int(model.launches_per_step * steps),
             "roofline": roofline,
@@ -365,6 +368,7 @@ def main() -> None:
     parser.add_argument("--prompt", type=int, default=2048)
     parser.add_argument("--decode", type=int, default=512)
     parser.add_argument("--lookahead", type=int, default=4)
+    parser.add_argument("--nccl-allreduce", action="store_true", help="tensor parallel: keep NCCL all-reduces (default: fused peer-memory exchange)")
     parser.add_argument("--layers", type=int, default=0, help="override the layer count (profiling aid; not a bench result)")
     parser.add_argument("--micro", default=None, help="MxK[xT]: time one linear shape alone (profiling aid)")
     parser.add_argument("--backend", type=int, default=5, help="prefill backend id for --micro with T >= 16")

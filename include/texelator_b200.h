@@ -168,6 +168,18 @@ int tx_kernel_status(int device, int clear);
  *                      floats; head_dim 128, at most 16384 positions
  *   silu_mul         : out[t,i] = silu(gate_up[t,i]) * gate_up[t,intermediate+i]                     */
 int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, int tokens, int hidden, float eps, void *stream);
+/* Tensor parallelism, one token: the all-reduce of a row-parallel linear's partial output fused into the
+ * residual add + RMSNorm that consumes it.  Every rank stores `partial` [hidden] into all ranks' inboxes
+ * over peer memory, publishes an epoch flag, waits (bounded; a wait that runs out records 32 in the
+ * status word read by tx_kernel_status) for the flags of all ranks and sums the inbox rows in rank order
+ * (fp32, one bf16 rounding, identical bits on every rank); then h += sum, y = rmsnorm(h) * weight.
+ * peer_inboxes[r] / peer_flags[r]: rank r's inbox (2 * world * hidden bf16, zero-initialised flags of
+ * 2 * world uint32) as addressable from this rank; `epoch_word`: a zero-initialised uint32 in this rank's
+ * memory that the kernel advances.  All ranks must make the same sequence of calls.  No reference
+ * counterpart (the reference is single-GPU). */
+int tx_aux_allreduce_add_rmsnorm(void *h, const void *partial, const void *weight, void *y, int hidden, float eps,
+                                 void *const *peer_inboxes, void *const *peer_flags, int rank, int world, void *epoch_word,
+                                 void *stream);
 int tx_aux_rope_append(void *qkv, const float *cos_table, const float *sin_table, const void *position, void *k_cache,
                        void *v_cache, int q_heads, int kv_heads, int head_dim, int max_len, void *stream);
 int tx_aux_attention_decode(const void *qkv, const void *k_cache, const void *v_cache, const void *position, float *scratch,

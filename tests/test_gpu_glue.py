@@ -184,3 +184,87 @@ def test_fused_linear_argument_checks(ext):
             ext.linear_fused_out(handle, x, y, swiglu=True)
     finally:
         ext.free(handle)
+
+
+class _LocalPeers:
+    """Stand-in for tp.PeerExchange on one GPU: `world` inboxes that all live in this GPU's memory, so the
+    test can play the other ranks' parts (write their inbox rows and flags) from the host side."""
+
+    def __init__(self, hidden, world, rank):
+        import ctypes
+        self.rank, self.world, self.hidden = rank, world, hidden
+        self.inboxes = [torch.zeros(2 * world * hidden, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+        self.flags = [torch.zeros(2 * world, device="cuda", dtype=torch.int32) for _ in range(world)]
+        self.epoch = torch.zeros(1, device="cuda", dtype=torch.int32)
+        pointers = ctypes.c_void_p * world
+        self.inbox_ptrs = pointers(*[t.data_ptr() for t in self.inboxes])
+        self.flag_ptrs = pointers(*[t.data_ptr() for t in self.flags])
+
+    def deliver(self, sender, epoch, values):
+        """What rank `sender` would have done for `epoch`: its row in our inbox, then its flag."""
+        slot = epoch & 1
+        start = (slot * self.world + sender) * self.hidden
+        self.inboxes[self.rank][start:start + self.hidden] = values.reshape(-1)
+        self.flags[self.rank][slot * self.world + sender] = epoch
+
+
+def test_allreduce_add_rmsnorm_single_rank_equals_plain_kernel(ext):
+    hidden = 5120
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    gamma = (1 + 0.1 * torch.randn(hidden, device="cuda", generator=gen)).bfloat16()
+    peers = _LocalPeers(hidden, 1, 0)
+    h = torch.randn(1, hidden, device="cuda", generator=gen).bfloat16()
+    h_ref = h.clone()
+    ext.kernel_status(clear=True)
+    for step in range(4):                                        # both inbox slots, advancing epochs
+        delta = torch.randn(1, hidden, device="cuda", generator=gen).bfloat16()
+        y, y_ref = torch.empty_like(h), torch.empty_like(h)
+        ext.allreduce_add_rmsnorm(h, delta, gamma, y, 1e-6, peers)
+        ext.add_rmsnorm(h_ref, delta, gamma, y_ref, 1e-6)
+        torch.cuda.synchronize()
+        assert torch.equal(h, h_ref) and torch.equal(y, y_ref), step
+        assert int(peers.epoch.item()) == step + 1
+    assert ext.kernel_status() == 0
+
+
+def test_allreduce_add_rmsnorm_sums_peers_in_rank_order(ext):
+    """Rank 1 of 3 with the other ranks' contributions already delivered: no kernel ever waits here."""
+    hidden, world, rank = 1024, 3, 1
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    gamma = (1 + 0.1 * torch.randn(hidden, device="cuda", generator=gen)).bfloat16()
+    peers = _LocalPeers(hidden, world, rank)
+    h = torch.randn(1, hidden, device="cuda", generator=gen).bfloat16()
+    ext.kernel_status(clear=True)
+    for epoch in (1, 2, 3):
+        parts = [torch.randn(1, hidden, device="cuda", generator=gen).bfloat16() for _ in range(world)]
+        for sender in range(world):
+            if sender != rank:
+                peers.deliver(sender, epoch, parts[sender])
+        total = (parts[0].float() + parts[1].float() + parts[2].float()).bfloat16()      # rank order, one rounding
+        h_ref, y_ref = h.clone(), torch.empty_like(h)
+        ext.add_rmsnorm(h_ref, total, gamma, y_ref, 1e-6)
+        y = torch.empty_like(h)
+        ext.allreduce_add_rmsnorm(h, parts[rank], gamma, y, 1e-6, peers)
+        torch.cuda.synchronize()
+        assert torch.equal(h, h_ref) and torch.equal(y, y_ref), epoch
+        slot = epoch & 1
+        for receiver in range(world):                            # our row and flag reached every rank's inbox
+            start = (slot * world + rank) * hidden
+            assert torch.equal(peers.inboxes[receiver][start:start + hidden], parts[rank].reshape(-1))
+            assert int(peers.flags[receiver][slot * world + rank].item()) == epoch
+    assert ext.kernel_status() == 0
+
+
+def test_allreduce_wait_is_bounded_and_reports(ext):
+    """A flag that nobody sets: the wait runs out, the kernel finishes, the status word says 32."""
+    hidden = 256
+    peers = _LocalPeers(hidden, 2, 0)
+    h = torch.zeros(1, hidden, device="cuda", dtype=torch.bfloat16)
+    gamma = torch.ones(hidden, device="cuda", dtype=torch.bfloat16)
+    ext.kernel_status(clear=True)
+    ext.allreduce_add_rmsnorm(h, torch.ones_like(h), gamma, torch.empty_like(h), 1e-6, peers)
+    torch.cuda.synchronize()
+    assert ext.kernel_status(clear=True) == 32
+    assert ext.kernel_status() == 0
+    torch.zeros(1, device="cuda").add_(1)                        # the context is still usable
+    torch.cuda.synchronize()

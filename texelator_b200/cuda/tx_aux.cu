@@ -82,6 +82,125 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16
   }
 }
 
+// ---- all-reduce fused into the residual add + RMSNorm (tensor parallelism, one token) -----------------
+// The row-parallel linears (o, down) leave a partial sum on every rank.  Instead of a collective followed
+// by the norm kernel, the norm kernel itself exchanges the partials over NVLink peer memory:
+//   1. every rank stores its partial into slot [epoch & 1][rank] of every rank's inbox (plain peer stores),
+//   2. fences at system scope and writes the epoch number into the matching flag word of every rank,
+//   3. waits -- bounded -- until its own flag words of all ranks show this epoch,
+//   4. sums the inbox rows in rank order (fp32, one bf16 rounding; every rank gets the same bits) and
+//      carries on with h += delta, y = rmsnorm(h) * weight.
+// The epoch lives in device memory and advances by one per call, so CUDA-graph replays keep working; two
+// inbox slots suffice because a rank can only start epoch e+1 after every peer has contributed to e.
+// No multicast objects, no TMA: peer loads and stores only.  A wait that runs out records code 32 in the
+// status word and the kernel finishes with whatever the inbox holds (the host sees the status).
+constexpr int kMaxRanks = 8;
+constexpr unsigned kPeerSpinLimit = 1u << 21;
+struct PeerTable {
+  uint4 *inbox[kMaxRanks];        // [2][world][hidden/8] on each rank, addressed from this rank
+  unsigned *flags[kMaxRanks];     // [2][world] on each rank
+};
+
+__global__ void __launch_bounds__(kNormThreads) allreduce_add_rmsnorm_kernel(__nv_bfloat16 *__restrict__ h,
+                                                                             const __nv_bfloat16 *__restrict__ partial,
+                                                                             const __nv_bfloat16 *__restrict__ weight,
+                                                                             __nv_bfloat16 *__restrict__ y, int hidden, float eps,
+                                                                             PeerTable peers, int rank, int world,
+                                                                             unsigned *__restrict__ epoch_word, int *__restrict__ status) {
+  __shared__ float partial_ss[kNormThreads / 32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int chunks = hidden / 8;
+  const unsigned epoch = __ldcg(epoch_word) + 1;
+  const unsigned slot = epoch & 1;
+  // 1. my partial -> every rank's inbox
+  const uint4 *src = reinterpret_cast<const uint4 *>(partial);
+  for (int i = threadIdx.x; i < chunks; i += kNormThreads) {
+    const uint4 v = __ldcg(src + i);
+    for (int p = 0; p < world; ++p) peers.inbox[p][(size_t(slot) * world + rank) * chunks + i] = v;
+  }
+  __syncthreads();
+  // 2. publish: the barrier orders the CTA's stores before thread 0's system-scope fence
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int p = 0; p < world; ++p)
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[p] + slot * world + rank), "r"(epoch) : "memory");
+  }
+  // 3. bounded wait for every rank's contribution to this epoch
+  if (threadIdx.x < world) {
+    const unsigned *flag = peers.flags[rank] + slot * world + threadIdx.x;
+    unsigned seen = 0, spin = 0;
+    for (; spin < kPeerSpinLimit; ++spin) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+      if (seen == epoch) break;
+    }
+    if (seen != epoch && status) atomicCAS(status, 0, 32);
+  }
+  __syncthreads();
+  // 4. delta = sum over ranks (rank order), h += delta, RMSNorm
+  const uint4 *inbox = peers.inbox[rank] + size_t(slot) * world * chunks;
+  uint4 *hr = reinterpret_cast<uint4 *>(h);
+  uint4 keep[kNormChunks];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    if (i < chunks) {
+      float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < world; ++r) {
+        const uint4 d = __ldcg(inbox + size_t(r) * chunks + i);     // written by a peer: read at L2
+        const __nv_bfloat162 *pd = reinterpret_cast<const __nv_bfloat162 *>(&d);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(pd[e]);
+          sum[2 * e] += f.x;
+          sum[2 * e + 1] += f.y;
+        }
+      }
+      uint4 v = __ldcg(hr + i);
+      __nv_bfloat162 *pv = reinterpret_cast<__nv_bfloat162 *>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __bfloat1622float2(pv[e]);
+        const float2 b = __bfloat1622float2(__floats2bfloat162_rn(sum[2 * e], sum[2 * e + 1]));   // the all-reduced bf16 delta
+        pv[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+      }
+      hr[i] = v;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __bfloat1622float2(pv[e]);
+        ss += a.x * a.x + a.y * a.y;
+      }
+      keep[c] = v;
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) partial_ss[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < kNormThreads / 32; ++w) total += partial_ss[w];
+  const float inv = rsqrtf(total / float(hidden) + eps);
+  const uint4 *wr = reinterpret_cast<const uint4 *>(weight);
+  uint4 *yr = reinterpret_cast<uint4 *>(y);
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    if (i < chunks) {
+      uint4 v = keep[c], w = wr[i], o;
+      const __nv_bfloat162 *pv = reinterpret_cast<const __nv_bfloat162 *>(&v), *pw = reinterpret_cast<const __nv_bfloat162 *>(&w);
+      __nv_bfloat162 *po = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __bfloat1622float2(pv[e]), g = __bfloat1622float2(pw[e]);
+        po[e] = __floats2bfloat162_rn(a.x * inv * g.x, a.y * inv * g.y);
+      }
+      yr[i] = o;
+    }
+  }
+  if (threadIdx.x == 0) *epoch_word = epoch;
+}
+
 // Rotate q and k of one token in place (rotate-half convention) and append k, v to the cache at the
 // position read from device memory.  qkv = [q_rows | kv_rows | kv_rows]; grid = heads (q + 2 kv).
 __global__ void __launch_bounds__(64) rope_append_kernel(__nv_bfloat16 *__restrict__ qkv, const float *__restrict__ cos_table,
@@ -540,6 +659,33 @@ int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, 
   TX_CUDA(launch_pdl(add_rmsnorm_kernel, dim3(tokens), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
                      static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(delta),
                      static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps));
+  count_launch();
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
+int tx_aux_allreduce_add_rmsnorm(void *h, const void *partial, const void *weight, void *y, int hidden, float eps,
+                                 void *const *peer_inboxes, void *const *peer_flags, int rank, int world, void *epoch_word,
+                                 void *stream) {
+  if (!h || !partial || !weight || !y || !peer_inboxes || !peer_flags || !epoch_word)
+    return fail(TX_EINVAL, "tx_aux_allreduce_add_rmsnorm: null argument");
+  if (hidden < 8 || hidden % 8 || hidden > kNormThreads * 8 * kNormChunks)
+    return fail(TX_EINVAL, "tx_aux_allreduce_add_rmsnorm: hidden must be a multiple of 8 and at most 16384");
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+    return fail(TX_EINVAL, "tx_aux_allreduce_add_rmsnorm: world must be 1..8 and rank inside it");
+  PeerTable table{};
+  for (int p = 0; p < world; ++p) {
+    if (!peer_inboxes[p] || !peer_flags[p]) return fail(TX_EINVAL, "tx_aux_allreduce_add_rmsnorm: null peer buffer");
+    table.inbox[p] = static_cast<uint4 *>(peer_inboxes[p]);
+    table.flags[p] = static_cast<unsigned *>(peer_flags[p]);
+  }
+  int device = 0;
+  TX_CUDA(cudaGetDevice(&device));
+  Workspace *ws = workspace_for(device);
+  TX_CUDA(launch_pdl(allreduce_add_rmsnorm_kernel, dim3(1), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
+                     static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(partial),
+                     static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps, table, rank, world,
+                     static_cast<unsigned *>(epoch_word), ws ? ws->status : nullptr));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;

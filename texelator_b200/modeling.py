@@ -228,6 +228,9 @@ class BC4Decoder:
                                                 self.ext.attention_step_scratch_floats(q_heads, max_len)),
                                             dtype=torch.float32, device=self.device)
             self.fused = c.head_dim == 128 and (c.q_heads // c.kv_heads) <= 8 and c.hidden <= 18432 and self.i_loc % 8 == 0
+        # tensor parallelism: the all-reduce of the o/down partials fused into the next residual add + norm
+        # over peer memory (tp.PeerExchange); None keeps the NCCL all-reduce
+        self.peers = None
         # residual add + RMSNorm inside the qkv and gate/up linears instead of separate launches: every CTA
         # of the linear then repeats the norm, which measured slower than the two small kernels on a B200
         self.fuse_norm = False
@@ -326,6 +329,32 @@ class BC4Decoder:
         self.tok.copy_(self.next_tok)
         self.pos.add_(1)
 
+    def _add_norm(self, residual, delta, weight):
+        """residual += delta (all-reduced first when it is a tensor-parallel partial); buf_x = rmsnorm(residual) * weight."""
+        if delta is not None and self.peers is not None and not self.fuse_norm:
+            self.ext.allreduce_add_rmsnorm(residual, delta, weight, self.buf_x, self.config.rms_eps, self.peers)
+        else:
+            self.ext.add_rmsnorm(residual, delta, weight, self.buf_x, self.config.rms_eps)
+
+    def enable_peer_exchange(self) -> bool:
+        """Switch the fused decode step of a tensor-parallel model from NCCL all-reduces to the all-reduce
+        fused into the norm kernel (collective call).  Returns False, keeping NCCL, when symmetric memory
+        cannot be set up on this system."""
+        if self.world == 1:
+            return False
+        from .tp import PeerExchange
+        try:
+            self.peers = PeerExchange(self.config.hidden, self.device, self.group)
+        except Exception as error:  # noqa: BLE001 - any set-up failure means "keep NCCL"
+            print(f"[texelator_b200] peer exchange unavailable, keeping NCCL all-reduce: {error}", flush=True)
+            self.peers = None
+        # all ranks must agree, or the call sequences diverge
+        flag = torch.tensor([1 if self.peers is not None else 0], device=self.device)
+        torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self.peers = None
+        return self.peers is not None
+
     def _decode_step_fused(self):
         """One decode step with the library's fused kernels, five launches per layer: qkv linear (with the
         residual add and RMSNorm in its activation staging), attention step (RoPE, cache append, attention,
@@ -337,7 +366,7 @@ class BC4Decoder:
         delta = None
         for layer in range(c.layers):
             if not self.fuse_norm:
-                ext.add_rmsnorm(residual, delta, self.norm1[layer], self.buf_x, c.rms_eps)
+                self._add_norm(residual, delta, self.norm1[layer])
                 ext.linear_out(self.h_qkv[layer], self.buf_x, self.buf_qkv)
             elif delta is None:
                 ext.linear_fused_out(self.h_qkv[layer], residual, self.buf_qkv, norm_weight=self.norm1[layer], eps=c.rms_eps)
@@ -348,20 +377,22 @@ class BC4Decoder:
             ext.attention_step(self.buf_qkv, self.cos, self.sin, self.pos, self.k_cache[layer], self.v_cache[layer],
                                self.attn_scratch, self.buf_attn, q_heads, kv_heads, c.head_dim)
             ext.linear_out(self.h_o[layer], self.buf_attn, self.buf_o)
-            self._reduce(self.buf_o)
+            if self.fuse_norm or self.peers is None:
+                self._reduce(self.buf_o)
             if self.fuse_norm:
                 ext.linear_fused_out(self.h_gu[layer], residual, self.buf_act, norm_weight=self.norm2[layer], delta=self.buf_o,
                                      eps=c.rms_eps, residual_out=spare, swiglu=True)
                 residual, spare = spare, residual
             else:
-                ext.add_rmsnorm(residual, self.buf_o, self.norm2[layer], self.buf_x, c.rms_eps)
+                self._add_norm(residual, self.buf_o, self.norm2[layer])
                 ext.linear_fused_out(self.h_gu[layer], self.buf_x, self.buf_act, swiglu=True)
             ext.linear_out(self.h_down[layer], self.buf_act, self.buf_down)
-            self._reduce(self.buf_down)
+            if self.fuse_norm or self.peers is None:
+                self._reduce(self.buf_down)
             delta = self.buf_down
         if residual is not self.buf_h:
             self.buf_h.copy_(residual)
-        ext.add_rmsnorm(self.buf_h, delta, self.final_norm, self.buf_x, c.rms_eps)
+        self._add_norm(self.buf_h, delta, self.final_norm)
         self.last_hidden.copy_(self.buf_x)
         logits = self.buf_x @ self.lm_head.T
         self.next_tok.copy_(logits.float().argmax(-1))

@@ -66,6 +66,7 @@ C_API = {
     "tx_aux_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, ctypes.c_float, _vp]),
     "tx_aux_rope_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "tx_aux_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp]),
+    "tx_aux_allreduce_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i32, ctypes.c_float, _vp, _vp, _i32, _i32, _vp, _vp]),
     "tx_aux_attention_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp]),
     "tx_aux_silu_mul": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "tx_launch_count": (ctypes.c_int64, []),
@@ -334,6 +335,16 @@ class _Extension:
         self._check(self._lib.tx_aux_attention_decode(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), position.data_ptr(),
                                                       scratch.data_ptr(), out.data_ptr(), q_heads, kv_heads, head_dim,
                                                       k_cache.shape[1], float(head_dim) ** -0.5, self._stream(qkv)))
+
+    def allreduce_add_rmsnorm(self, h: torch.Tensor, partial: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, eps: float,
+                              peers) -> None:
+        """``h += all_reduce(partial)``; ``y = rmsnorm(h) * weight`` for one token in one launch; ``peers`` is a
+        ``tp.PeerExchange`` (peer-mapped inboxes and flags of all ranks)."""
+        if h.numel() != weight.numel() or partial.numel() != h.numel():
+            raise RuntimeError("fused all-reduce handles exactly one token")
+        self._check(self._lib.tx_aux_allreduce_add_rmsnorm(h.data_ptr(), partial.data_ptr(), weight.data_ptr(), y.data_ptr(),
+                                                           h.numel(), float(eps), peers.inbox_ptrs, peers.flag_ptrs, peers.rank,
+                                                           peers.world, peers.epoch.data_ptr(), self._stream(h)))
 
     @staticmethod
     def attention_step_scratch_floats(q_heads: int, max_len: int) -> int:

@@ -104,3 +104,37 @@ def install_tp(model: nn.Module, weights: Path, rank: int, world: int, group=Non
         raise
     model._texelator_handles = handles
     return handles
+
+
+class PeerExchange:
+    """Peer-mapped buffers for ``tx_aux_allreduce_add_rmsnorm``: every rank owns an inbox of
+    ``2 * world * hidden`` bf16 values and ``2 * world`` flag words in symmetric memory
+    (``torch.distributed._symmetric_memory``: plain peer mappings over NVLink, no multicast object is
+    bound), plus a local epoch word.  ``inbox_ptrs`` / ``flag_ptrs`` are ctypes arrays with the address of
+    every rank's buffer as seen from this rank.  Construction is collective over ``group`` and raises when
+    symmetric memory cannot be set up, in which case callers keep the NCCL all-reduce.
+    """
+
+    def __init__(self, hidden: int, device: torch.device, group=None):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("the fused all-reduce handles up to 8 ranks")
+        with torch.cuda.device(device):
+            self.inbox = symm_mem.empty(2 * self.world * hidden, dtype=torch.bfloat16, device=device)
+            self.flags = symm_mem.empty(2 * self.world, dtype=torch.int32, device=device)
+            self.inbox.zero_()
+            self.flags.zero_()
+            inbox_handle = symm_mem.rendezvous(self.inbox, group)
+            flag_handle = symm_mem.rendezvous(self.flags, group)
+            self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+            torch.cuda.synchronize(device)
+        dist.barrier(group)            # every rank's zeroes are in place before anyone publishes a flag
+        pointers = ctypes.c_void_p * self.world
+        self.inbox_ptrs = pointers(*[int(p) for p in inbox_handle.buffer_ptrs])
+        self.flag_ptrs = pointers(*[int(p) for p in flag_handle.buffer_ptrs])
+        self._handles = (inbox_handle, flag_handle)     # keep the mappings alive
