@@ -1,0 +1,106 @@
+"""Parity at the benchmark's full matrix sizes (27B-class shapes), through checks whose cost does not grow
+with the matrix: oracle on a sample of rows, two independent GPU decoders against each other, round trips
+and sharding identities."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import bc4_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(34816, 5120), (5120, 17408), (7168, 5120)]      # gate+up, down, q+k+v of the 27B-class model
+
+
+@pytest.fixture(scope="module")
+def ext():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from texelator_b200 import runtime
+    return runtime.extension()
+
+
+def _encode(m, k, seed):
+    from texelator_b200.modeling import encode_minmax_cuda, software_palette_table
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    weight = torch.randn(m, k, device="cuda", generator=gen) * 0.02
+    weight[torch.rand(m, k, device="cuda", generator=gen) < 0.002] = 0       # a few low-mode blocks now and then
+    blocks, scales = encode_minmax_cuda(weight, software_palette_table("cuda"))
+    x = torch.randn(1, k, device="cuda", generator=gen).bfloat16()
+    return blocks, scales, x
+
+
+@pytest.mark.parametrize("m,k", SHAPES)
+def test_full_size_round_trip_sample_rows_and_decoder_agreement(ext, lut, m, k):
+    blocks, scales, x = _encode(m, k, m + k)
+    handle = ext.pack_encoded_device(blocks, scales)
+    try:
+        # 1. pack -> unpack returns the encoded bytes (an endpoint of -128 comes back as -127, the same value)
+        original = blocks.cpu().numpy().reshape(-1, 8).copy()
+        endpoints = original[:, :2].view(np.int8)
+        endpoints[endpoints == -128] = -127
+        assert np.array_equal(ext.unpack_blocks(handle).numpy().reshape(-1, 8), original)
+        # 2. the tensor-core decoder against the CPU oracle on 96 sampled rows
+        y = ext.linear(handle, x)
+        rows = np.sort(np.random.default_rng(m).choice(m, 96, replace=False))
+        per_row = k // 16
+        sample_blocks = original.reshape(m, per_row * 8)[rows].reshape(-1)
+        sample_scales = scales.cpu().numpy()[rows]
+        ref = O.linear_bf16(x.float().cpu().numpy(), sample_blocks, sample_scales, lut)
+        got = y.float().cpu().numpy()[:, rows]
+        assert O.rel_rms(got, ref) <= 1e-2
+        # 3. ... and against the GPU kernel that uses the reference's per-weight arithmetic, on every row
+        ext.set_decode_path(handle, 1)
+        exact = ext.linear(handle, x)
+        ext.set_decode_path(handle, 0)
+        assert O.rel_rms(exact.float().cpu().numpy()[:, rows], ref) <= 4e-3
+        assert O.rel_rms(y.float().cpu().numpy(), exact.float().cpu().numpy()) <= 1e-2
+        # 4. determinism and look-ahead independence (summation order is fixed by the tile walk)
+        for lookahead in (1, 2, 8):
+            ext.set_lookahead(handle, lookahead)
+            assert torch.equal(ext.linear(handle, x), y), lookahead
+    finally:
+        ext.free(handle)
+
+
+def test_full_size_prefill_tile_agrees_with_decode_kernel(ext):
+    """512 tokens through the tcgen05 tile and the same tokens one by one through the decode GEMV: both multiply
+    exact integer numerators by identically rescaled activations, so only the fp32 summation order differs."""
+    m, k = 17408, 5120
+    blocks, scales, _ = _encode(m, k, 77)
+    handle = ext.pack_encoded_device(blocks, scales)
+    try:
+        gen = torch.Generator(device="cuda").manual_seed(78)
+        x = torch.randn(512, k, device="cuda", generator=gen).bfloat16()
+        ext.set_prefill(handle, 16, 32768)
+        outputs = {}
+        for backend in (5, 6, 7):
+            ext.set_prefill_backend(handle, backend)
+            outputs[backend] = ext.linear(handle, x)
+        assert torch.equal(outputs[5], outputs[6]) and torch.equal(outputs[5], outputs[7])
+        for token in (0, 255, 511):
+            single = ext.linear(handle, x[token:token + 1].contiguous())
+            a, b = outputs[5][token].float(), single[0].float()
+            assert float((a - b).norm() / b.norm()) <= 2e-3, token
+        assert ext.kernel_status() == 0
+    finally:
+        ext.free(handle)
+
+
+def test_full_size_row_shards_reassemble_bit_exactly(ext):
+    """Column-parallel sharding is byte slicing: the outputs of 8 row shards concatenate to the unsharded output."""
+    m, k, world = 34816, 5120, 8
+    blocks, scales, x = _encode(m, k, 91)
+    handle = ext.pack_encoded_device(blocks, scales)
+    shards = []
+    try:
+        full = ext.linear(handle, x)
+        host_blocks, host_scales = blocks.cpu(), scales.cpu()
+        per = m // world
+        for rank in range(world):
+            shards.append(ext.pack_encoded_shard(host_blocks, host_scales, m, k, (rank * per, (rank + 1) * per), (0, k // 16)))
+        parts = [ext.linear(h, x) for h in shards]
+        assert torch.equal(torch.cat(parts, 1), full)
+    finally:
+        for h in shards + [handle]:
+            ext.free(h)
