@@ -140,6 +140,16 @@ def cpu_baseline_sample(config, seconds: float = 10.0) -> dict:
             "seconds": elapsed}
 
 
+def workload_config(config, prompt: int, world: int, lookahead: int) -> dict:
+    """The `config` object of the JSON line: the same workload description for both arms."""
+    return {"workload": f"{config.name} dense decoder, batch-1 decode after a {prompt}-token random-id prompt",
+            "model_shape": config.name, "hidden": config.hidden, "layers": config.layers,
+            "intermediate": config.intermediate, "parallelism": f"tp{world}",
+            "bc4_bytes_per_token": config.bc4_bytes_per_token(),
+            "l2": "per-token weight stream (>=1.3 GB per GPU) is larger than L2; no flush needed",
+            "lookahead": lookahead}
+
+
 def run_reference_arm(args, config) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -156,7 +166,8 @@ def run_reference_arm(args, config) -> None:
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{config.name} batch-1 decode, CPU dequantise-then-matmul sample", "model_shape": config.name},
+            "config": dict(workload_config(config, args.prompt, args.gpus, args.lookahead),
+                           note="reference arm: CPU dequantise-then-matmul on a bounded slab of this workload, extrapolated by bytes"),
             "cpu_baseline": best,
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -290,14 +301,9 @@ def run_gpu_arm(args, config) -> None:
             "metric": METRIC, "value": 1000.0 / ms, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": f"{config.name} dense decoder, batch-1 decode after a {prompt}-token random-id prompt",
-                       "model_shape": config.name, "hidden": config.hidden, "layers": config.layers,
-                       "intermediate": config.intermediate, "parallelism": f"tp{world}",
-                       "bc4_bytes_per_token": config.bc4_bytes_per_token(),
-                       "l2": "per-token weight stream (>=1.3 GB per GPU) is larger than L2; no flush needed",
-                       "lookahead": args.lookahead,
-                       "allreduce": ("none" if world == 1 else
-                                     "fused into the norm kernel over NVLink peer memory" if fused_allreduce else "nccl")},
+            "config": dict(workload_config(config, prompt, world, args.lookahead),
+                           allreduce=("none" if world == 1 else
+                                      "fused into the norm kernel over NVLink peer memory" if fused_allreduce else "nccl")),
             "e2e": {"value": 1000.0 / ms_e2e, "unit": UNIT, "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
             "gpu_launches": int(model.launches_per_step * steps),
             "roofline": roofline,
