@@ -281,6 +281,7 @@ gemv_tile_kernel(const GemvParams p) {
   auto load_row_constants = [&](int rt) {
 #pragma unroll
     for (int j = 0; j < kPerThread; ++j) {
+      if (j * workers >= kElems) break;        // uniform: with eight worker warps only j = 0 exists
       int e = tid + j * workers;
       int row = rt * 16 + ((e >> 6) & 1) * 8 + ((e & 31) >> 2);
       int tok = (e >> 7) * 8 + 2 * (e & 3) + ((e >> 5) & 1);
@@ -349,6 +350,7 @@ gemv_tile_kernel(const GemvParams p) {
         asm volatile("bar.sync 1, %0;" ::"r"(workers) : "memory");
 #pragma unroll
         for (int j = 0; j < kPerThread; ++j) {
+          if (j * workers >= kElems) break;    // uniform
           const int e = tid + j * workers;
           if (row_live[j]) {
             const float *src = part_g + buf * kGemvWarps * kElems + e;
