@@ -121,24 +121,23 @@ gemv_tile_kernel(const GemvParams p) {
   // -- first loads, issued before anything else.  The prefetch pointer walks this warp's units
   //    (ki = warp, warp + WS, ... of tiles blockIdx.x, + gridDim.x, ...) and stops at the end of the payload.
   const int tile_stride = gridDim.x;
-  const long long first_unit = (long long)blockIdx.x * KI + warp;
-  const uint4 *pnext = p.tiles + first_unit * 64 + lane;
-  const uint8_t *fnext = p.flags + first_unit;
-  const uint4 *const plimit = p.tiles + (long long)MT * KI * 64;
-  const long long step_unit = WS, step_tile = (long long)tile_stride * KI - (long long)(per_tile - 1) * WS;
+  // The walk is kept as a 32-bit unit index (payloads stay far below 2^32 units) and stops loading at the
+  // end of the payload.
+  const unsigned unit_limit = unsigned(MT) * unsigned(KI);
+  unsigned unext = unsigned(blockIdx.x) * unsigned(KI) + unsigned(warp);
+  const unsigned step_unit = WS, step_tile = unsigned(tile_stride) * unsigned(KI) - unsigned(per_tile - 1) * unsigned(WS);
   int pcount = 0;
   uint4 pend[LOOKAHEAD][2];
   unsigned pflag[LOOKAHEAD];
   auto prefetch = [&](int slot) {
-    if (worker && pnext < plimit) {
-      pend[slot][0] = ldg_stream(pnext);
-      pend[slot][1] = ldg_stream(pnext + 32);
-      pflag[slot] = *fnext;
+    if (unext < unit_limit) {                  // (one shared padding unit would be a hot spot for every warp's tail)
+      const uint4 *src = p.tiles + size_t(unext) * 64 + lane;
+      pend[slot][0] = ldg_stream(src);
+      pend[slot][1] = ldg_stream(src + 32);
+      if (LOWMODE) pflag[slot] = p.flags[unext];
     }
     const bool wrap = pcount == per_tile - 1;
-    const long long advance = wrap ? step_tile : step_unit;
-    pnext += advance * 64;
-    fnext += advance;
+    unext += wrap ? step_tile : step_unit;
     pcount = wrap ? 0 : pcount + 1;
   };
 #pragma unroll
@@ -355,7 +354,12 @@ gemv_tile_kernel(const GemvParams p) {
           if (row_live[j]) {
             const float *src = part_g + buf * kGemvWarps * kElems + e;
             float sum = 0.f;
-            for (int w = 0; w < WS; ++w) sum += src[w * kElems];
+            if (WS == kGemvWarps) {              // the usual case, unrolled; same order either way
+#pragma unroll
+              for (int w = 0; w < kGemvWarps; ++w) sum += src[w * kElems];
+            } else {
+              for (int w = 0; w < WS; ++w) sum += src[w * kElems];
+            }
             const int c = e >> 5, ln = e & 31;
             const int row = tile * 16 + ((c >> 1) & 1) * 8 + (ln >> 2);
             const int tok = (c >> 2) * 8 + 2 * (ln & 3) + (c & 1);
@@ -363,7 +367,12 @@ gemv_tile_kernel(const GemvParams p) {
               // element e + 64 is the up row of this gate row; both are rounded to bf16 first, like the
               // outputs of an unfused linear, then combined with silu_mul's arithmetic
               float up_sum = 0.f;
-              for (int w = 0; w < WS; ++w) up_sum += src[w * kElems + 64];
+              if (WS == kGemvWarps) {
+#pragma unroll
+                for (int w = 0; w < kGemvWarps; ++w) up_sum += src[w * kElems + 64];
+              } else {
+                for (int w = 0; w < WS; ++w) up_sum += src[w * kElems + 64];
+              }
               const float gate = __bfloat162float(__float2bfloat16(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j])));
               const float up = __bfloat162float(__float2bfloat16(fmaf(up_sum, up_scale[j] * tokmul[tok], up_bias[j])));
               p.y[size_t(tok) * (p.M / 2) + tile * 8 + (ln >> 2)] = __float2bfloat16(gate / (1.f + __expf(-gate)) * up);
