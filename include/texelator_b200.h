@@ -165,7 +165,7 @@ int tx_kernel_status(int device, int clear);
  *                      holds q_heads * ceil(max_len/128) * (head_dim+2) floats; head_dim must be 128
  *   attention_step   : rope_append + attention_decode of one token in ONE launch (q is rotated on the
  *                      fly, qkv is left untouched); `scratch` holds q_heads * ceil(max_len/64) * 132
- *                      floats; head_dim 128, at most 16384 positions
+ *                      floats; head_dim 128; long caches are walked in 64-key chunks per CTA
  *   silu_mul         : out[t,i] = silu(gate_up[t,i]) * gate_up[t,intermediate+i]                     */
 int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, int tokens, int hidden, float eps, void *stream);
 /* Tensor parallelism, one token: the all-reduce of a row-parallel linear's partial output fused into the

@@ -39,6 +39,8 @@ def _reference_step(qkv, cos, sin, pos, k_cache, v_cache, q_heads, kv_heads, hea
     (8, 8, 130, [0, 64, 129]),
     (16, 2, 320, [5, 127, 128, 319]),
     (5, 1, 700, [640]),                                      # one rank of an 8-way tensor-parallel split
+    (40, 8, 9000, [2367, 2368, 4500, 8999]),                 # more chunks than resident CTAs: several chunks per CTA
+    (5, 1, 20000, [16383, 19999]),                           # 313 chunks on 256 CTAs
 ])
 def test_attention_step_matches_pytorch(ext, q_heads, kv_heads, max_len, positions):
     head_dim = 128

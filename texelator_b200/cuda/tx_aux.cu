@@ -3,6 +3,8 @@
 // this to Hugging Face / PyTorch (texelator/cli.py:189-219); at batch 1 on a B200 those many small
 // PyTorch kernels cost more than the weight stream, so the decoder harness replaces them with a few
 // fused launches.  No reference counterpart; bf16 in and out, fp32 arithmetic.
+#include <algorithm>
+
 #include "tx_common.cuh"
 
 namespace tx {
@@ -623,6 +625,259 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_kernel(const _
   }
 }
 
+// The same step for long caches: the grid is capped at two resident CTAs per SM and every CTA walks several
+// 64-key chunks (chunk = split, split + gridDim.x, ...) with running soft-max statistics.
+template <int GROUP>
+__global__ void __launch_bounds__(kStepThreads, 2) attention_step_loop_kernel(const __nv_bfloat16 *__restrict__ qkv,
+                                                                      const float *__restrict__ cos_table,
+                                                                      const float *__restrict__ sin_table,
+                                                                      const long long *__restrict__ position,
+                                                                      __nv_bfloat16 *__restrict__ k_cache,
+                                                                      __nv_bfloat16 *__restrict__ v_cache, float *__restrict__ partial,
+                                                                      __nv_bfloat16 *__restrict__ out, int q_heads, int kv_heads,
+                                                                      int max_len, int split_capacity, float scale) {
+  __shared__ __align__(16) float q_s[GROUP][kHeadDim];
+  __shared__ float p_s[GROUP][kStepKeys];
+  __shared__ __align__(16) float red_s[kStepThreads / 32][GROUP][kHeadDim];   // per-warp partial sums
+  __shared__ float stat_s[GROUP][2];
+  __shared__ float rescale_s[GROUP];
+  __shared__ float weight_s[GROUP][kStepMaxSplits];   // merge weights of the splits
+  __shared__ int last_s;
+  constexpr int kHalf = kHeadDim / 2, kWarps = kStepThreads / 32;
+  const int split = blockIdx.x, kvh = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const long long pos = __ldcg(position);                       // attends to keys 0..pos; key pos is new
+  const int chunks = int(pos / kStepKeys) + 1;                  // 64-key chunks that hold at least one key
+  const int splits = gridDim.x;                                 // CTA `split` takes chunks split, split + splits, ...
+  const int live = min(splits, chunks);                         // CTAs with work
+  if (split >= live) return;
+  const size_t q_rows = size_t(q_heads) * kHeadDim, kv_rows = size_t(kv_heads) * kHeadDim;
+
+  // ---- prologue: rotate-half RoPE of q (and of the new key by its owner) ----
+  for (int idx = tid; idx < GROUP * kHalf; idx += kStepThreads) {
+    const int g = idx / kHalf, i = idx % kHalf;
+    const float c = cos_table[pos * kHalf + i], sn = sin_table[pos * kHalf + i];
+    const __nv_bfloat16 *vec = qkv + size_t(kvh * GROUP + g) * kHeadDim;
+    const float x1 = __bfloat162float(__ldcg(vec + i)), x2 = __bfloat162float(__ldcg(vec + i + kHalf));
+    q_s[g][i] = __bfloat162float(__float2bfloat16(x1 * c - x2 * sn)) * scale;
+    q_s[g][i + kHalf] = __bfloat162float(__float2bfloat16(x2 * c + x1 * sn)) * scale;
+  }
+  if (split == (chunks - 1) % splits) {          // the CTA whose last chunk holds the new position
+    if (tid < kHalf) {
+      const int i = tid;
+      const float c = cos_table[pos * kHalf + i], sn = sin_table[pos * kHalf + i];
+      const __nv_bfloat16 *vec = qkv + q_rows + size_t(kvh) * kHeadDim;
+      const float x1 = __bfloat162float(__ldcg(vec + i)), x2 = __bfloat162float(__ldcg(vec + i + kHalf));
+      __nv_bfloat16 *dst = k_cache + (size_t(kvh) * max_len + pos) * kHeadDim;
+      dst[i] = __float2bfloat16(x1 * c - x2 * sn);
+      dst[i + kHalf] = __float2bfloat16(x2 * c + x1 * sn);
+    } else if (tid < 2 * kHalf) {
+      const int i = tid - kHalf;
+      const __nv_bfloat162 *vec = reinterpret_cast<const __nv_bfloat162 *>(qkv + q_rows + kv_rows + size_t(kvh) * kHeadDim);
+      reinterpret_cast<__nv_bfloat162 *>(v_cache + (size_t(kvh) * max_len + pos) * kHeadDim)[i] = __ldcg(vec + i);
+    }
+  }
+  __syncthreads();
+
+  // ---- all cache rows of a chunk in flight at once ----
+  // keys: lane (r = lane >> 3, j = lane & 7) holds dimensions 8j..8j+7 and 64+8j..64+8j+7 of key
+  // warp*8 + batch*4 + r; values: lane holds dimensions 4*lane..4*lane+3 of key warp*8 + i
+  const int r = lane >> 3, j = lane & 7;
+  uint4 key_raw[2][2];
+  uint2 val_raw[8];
+  auto request_keys = [&](int chunk) {
+    const int key0 = chunk * kStepKeys;
+    const int count = int(min((long long)kStepKeys, pos + 1 - key0));
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      const int key = warp * 8 + b * 4 + r;
+      const uint4 *row = reinterpret_cast<const uint4 *>(k_cache + (size_t(kvh) * max_len + key0 + key) * kHeadDim);
+      key_raw[b][0] = key < count ? __ldcg(row + j) : make_uint4(0, 0, 0, 0);
+      key_raw[b][1] = key < count ? __ldcg(row + 8 + j) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  auto request_values = [&](int chunk) {
+    const int key0 = chunk * kStepKeys;
+    const int count = int(min((long long)kStepKeys, pos + 1 - key0));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int key = warp * 8 + i;
+      val_raw[i] = key < count ? __ldcg(reinterpret_cast<const uint2 *>(v_cache + (size_t(kvh) * max_len + key0 + key) * kHeadDim) + lane)
+                               : make_uint2(0, 0);
+    }
+  };
+  request_keys(split);
+  request_values(split);
+
+  // Long caches give a CTA several chunks: running soft-max statistics per head (kept by warp g for head
+  // g), accumulators rescaled when the maximum moves, the next chunk's rows requested before this one is
+  // processed.  With one chunk per CTA (up to about 2300 positions on 8 kv heads) the loop runs once.
+  // The next chunk's keys are requested as soon as this chunk's scores are done with the key registers,
+  // its values after the value registers are consumed (no second register set: two CTAs per SM).
+  float acc[GROUP][4];
+#pragma unroll
+  for (int g = 0; g < GROUP; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+  float run_max = -INFINITY, run_sum = 0.f;
+  for (int chunk = split; chunk < chunks; chunk += splits) {
+  const int count = int(min((long long)kStepKeys, pos + 1 - (long long)chunk * kStepKeys));
+  const bool more = chunk + splits < chunks;                    // uniform
+  // ---- scores (q of one head at a time, so that two CTAs fit the register file of an SM) ----
+  {
+    float k[2][16];
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      unpack_bf16x8(key_raw[b][0], *reinterpret_cast<float(*)[8]>(&k[b][0]));
+      unpack_bf16x8(key_raw[b][1], *reinterpret_cast<float(*)[8]>(&k[b][8]));
+    }
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+      const float4 *src = reinterpret_cast<const float4 *>(&q_s[g][0]);
+      const float4 qa = src[2 * j], qb = src[2 * j + 1], qc = src[16 + 2 * j], qd = src[16 + 2 * j + 1];
+      const float q[16] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w, qc.x, qc.y, qc.z, qc.w, qd.x, qd.y, qd.z, qd.w};
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        const int key = warp * 8 + b * 4 + r;
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) dot = fmaf(k[b][e], q[e], dot);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        if (j == 0) p_s[g][key] = key < count ? dot : -INFINITY;
+      }
+    }
+  }
+  if (more) request_keys(chunk + splits);
+  __syncthreads();
+  // ---- per head: max and exp-sum over the CTA's keys (warp g handles head g; GROUP <= 8 warps) ----
+  if (warp < GROUP) {
+    const float a = p_s[warp][lane], b = p_s[warp][lane + 32];
+    const float m = fmaxf(run_max, warp_max(fmaxf(a, b)));     // finite: every chunk of the walk holds a key
+    const float ea = __expf(a - m), eb = __expf(b - m);
+    p_s[warp][lane] = ea;
+    p_s[warp][lane + 32] = eb;
+    const float factor = __expf(run_max - m);                   // 0 on the first chunk
+    run_sum = fmaf(run_sum, factor, warp_sum(ea + eb));
+    run_max = m;
+    if (lane == 0) {
+      stat_s[warp][0] = m;
+      stat_s[warp][1] = run_sum;
+      rescale_s[warp] = factor;
+    }
+  }
+  __syncthreads();
+  // ---- values ----
+  {
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+      const float factor = rescale_s[g];
+      acc[g][0] *= factor; acc[g][1] *= factor; acc[g][2] *= factor; acc[g][3] *= factor;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float v0 = __uint_as_float(val_raw[i].x << 16), v1 = __uint_as_float(val_raw[i].x & 0xffff0000u);
+      const float v2 = __uint_as_float(val_raw[i].y << 16), v3 = __uint_as_float(val_raw[i].y & 0xffff0000u);
+#pragma unroll
+      for (int g = 0; g < GROUP; ++g) {
+        const float pw = p_s[g][warp * 8 + i];
+        acc[g][0] = fmaf(pw, v0, acc[g][0]);
+        acc[g][1] = fmaf(pw, v1, acc[g][1]);
+        acc[g][2] = fmaf(pw, v2, acc[g][2]);
+        acc[g][3] = fmaf(pw, v3, acc[g][3]);
+      }
+    }
+  }
+  if (more) {
+    request_values(chunk + splits);
+    __syncthreads();                                            // p_s and rescale_s are rewritten by the next chunk
+  }
+  }   // chunk loop
+#pragma unroll
+  for (int g = 0; g < GROUP; ++g)
+    *reinterpret_cast<float4 *>(&red_s[warp][g][4 * lane]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+  __syncthreads();
+  for (int idx = tid; idx < GROUP * kHeadDim; idx += kStepThreads) {
+    const int g = idx / kHeadDim, d = idx % kHeadDim;
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) sum += red_s[w][g][d];
+    partial[(size_t(kvh * GROUP + g) * split_capacity + split) * kStepRow + d] = sum;
+  }
+  if (tid < GROUP) {
+    float *rec = partial + (size_t(kvh * GROUP + tid) * split_capacity + split) * kStepRow;
+    rec[kHeadDim] = stat_s[tid][0];
+    rec[kHeadDim + 1] = stat_s[tid][1];
+  }
+  // ---- publish; the CTA that arrives last for this kv head merges ----
+  // The barrier makes every thread's stores visible to thread 0, whose device-scope fence orders them
+  // before its arrival (the grid-synchronisation idiom); the last arriver fences again before reading.
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned before = atomicAdd(&g_attention_arrivals[kvh], 1u);
+    last_s = before == unsigned(live - 1);
+    if (last_s) {
+      g_attention_arrivals[kvh] = 0;      // every CTA of this launch has arrived: ready for the next launch
+      __threadfence();
+    }
+  }
+  __syncthreads();
+  if (!last_s) return;
+  // merge: warps 0..GROUP-1 turn the (max, sum) records of their head into weights (each record is read
+  // once, eight per lane at most); then all warps accumulate weighted outputs over interleaved splits
+  // and the CTA adds the eight partial sums
+  if (warp < GROUP) {
+    const float *base = partial + size_t(kvh * GROUP + warp) * split_capacity * kStepRow;
+    constexpr int kPerLane = kStepMaxSplits / 32;
+    float2 rec[kPerLane];
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int sp = lane + 32 * i;
+      rec[i] = sp < live ? __ldcg(reinterpret_cast<const float2 *>(base + size_t(sp) * kStepRow + kHeadDim)) : make_float2(-INFINITY, 0.f);
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) m = fmaxf(m, rec[i].x);
+    m = warp_max(m);
+    float den = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int sp = lane + 32 * i;
+      const float w = __expf(rec[i].x - m);        // 0 for the padding records
+      if (sp < live) weight_s[warp][sp] = w;
+      den = fmaf(w, rec[i].y, den);
+    }
+    den = warp_sum(den);
+    if (lane == 0) stat_s[warp][0] = 1.f / den;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int g = 0; g < GROUP; ++g) {
+    const float *base = partial + size_t(kvh * GROUP + g) * split_capacity * kStepRow;
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int sp = warp; sp < live; sp += kWarps) {
+      const float w = weight_s[g][sp];
+      const float4 v = __ldcg(reinterpret_cast<const float4 *>(base + size_t(sp) * kStepRow) + lane);
+      num.x = fmaf(w, v.x, num.x);
+      num.y = fmaf(w, v.y, num.y);
+      num.z = fmaf(w, v.z, num.z);
+      num.w = fmaf(w, v.w, num.w);
+    }
+    *reinterpret_cast<float4 *>(&red_s[warp][g][4 * lane]) = num;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < GROUP * kHeadDim; idx += kStepThreads) {
+    const int g = idx / kHeadDim, d = idx % kHeadDim;
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) sum += red_s[w][g][d];
+    out[size_t(kvh * GROUP + g) * kHeadDim + d] = __float2bfloat16(sum * stat_s[g][0]);
+  }
+}
+
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i]
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16 *__restrict__ gu, __nv_bfloat16 *__restrict__ out,
                                                        int inter, int tokens) {
@@ -639,10 +894,13 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16 *__re
   }
 }
 
-template <int GROUP>
+template <int GROUP, bool LOOP>
 static cudaError_t launch_attention_step(int splits, int kv_heads, cudaStream_t s, const __nv_bfloat16 *qkv, const float *cos_table,
                                          const float *sin_table, const long long *position, __nv_bfloat16 *k_cache,
                                          __nv_bfloat16 *v_cache, float *scratch, __nv_bfloat16 *out, int q_heads, int max_len, float scale) {
+  if (LOOP)
+    return launch_pdl(attention_step_loop_kernel<GROUP>, dim3(splits, kv_heads), dim3(kStepThreads), 0, s, qkv, cos_table, sin_table, position,
+                      k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale);
   return launch_pdl(attention_step_kernel<GROUP>, dim3(splits, kv_heads), dim3(kStepThreads), 0, s, qkv, cos_table, sin_table, position,
                     k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale);
 }
@@ -730,8 +988,16 @@ int tx_aux_attention_step(const void *qkv, const float *cos_table, const float *
     return fail(TX_EINVAL, "tx_aux_attention_step: null argument");
   if (head_dim != kHeadDim || kv_heads < 1 || kv_heads > kStepMaxKvHeads || q_heads % kv_heads || q_heads / kv_heads > kMaxGroup)
     return fail(TX_EUNSUPPORTED, "tx_aux_attention_step supports head_dim 128, up to 128 kv heads and up to 8 query heads per kv head");
-  const int splits = (max_len + kStepKeys - 1) / kStepKeys;
-  if (max_len < 1 || splits > kStepMaxSplits) return fail(TX_EUNSUPPORTED, "tx_aux_attention_step supports caches of up to 16384 positions");
+  if (max_len < 1) return fail(TX_EINVAL, "tx_aux_attention_step: max_len must be positive");
+  // one CTA per 64-key chunk while that fits two resident CTAs per SM; longer caches give every CTA several chunks
+  int device = 0;
+  TX_CUDA(cudaGetDevice(&device));
+  Workspace *ws = workspace_for(device);
+  const int resident = std::max(1, (ws ? 2 * ws->sm_count : 256) / kv_heads);
+  const int chunks_max = (max_len + kStepKeys - 1) / kStepKeys;
+  // up to two waves of one-chunk CTAs (most of them idle while the cache is short) run the leaner variant
+  const bool loop = chunks_max > 2 * resident || chunks_max > kStepMaxSplits;
+  const int splits = loop ? std::min(std::min(chunks_max, resident), kStepMaxSplits) : chunks_max;
   auto s = static_cast<cudaStream_t>(stream);
   auto q = static_cast<const __nv_bfloat16 *>(qkv);
   auto pos = static_cast<const long long *>(position);
@@ -739,8 +1005,13 @@ int tx_aux_attention_step(const void *qkv, const float *cos_table, const float *
   auto o = static_cast<__nv_bfloat16 *>(out);
   cudaError_t err = cudaSuccess;
   switch (q_heads / kv_heads) {
-#define TX_STEP_CASE(G) \
-  case G: err = launch_attention_step<G>(splits, kv_heads, s, q, cos_table, sin_table, pos, kc, vc, scratch, o, q_heads, max_len, scale); break;
+#define TX_STEP_CASE(G)                                                                                                          \
+  case G:                                                                                                                        \
+    err = loop ? launch_attention_step<G, true>(splits, kv_heads, s, q, cos_table, sin_table, pos, kc, vc, scratch, o, q_heads,  \
+                                                max_len, scale)                                                                  \
+               : launch_attention_step<G, false>(splits, kv_heads, s, q, cos_table, sin_table, pos, kc, vc, scratch, o, q_heads, \
+                                                 max_len, scale);                                                                \
+    break;
     TX_STEP_CASE(1) TX_STEP_CASE(2) TX_STEP_CASE(3) TX_STEP_CASE(4) TX_STEP_CASE(5) TX_STEP_CASE(6) TX_STEP_CASE(7) TX_STEP_CASE(8)
 #undef TX_STEP_CASE
     default: return fail(TX_EUNSUPPORTED, "tx_aux_attention_step: unsupported query group");
