@@ -260,9 +260,9 @@ def gemv_roofline(model, config, world: int) -> dict:
     peak, source = measured_peaks()
     achieved = total / ms / 1e6
     # DRAM bytes per algorithmic byte of this kernel, from the ncu capture of one 34816x5120 launch
-    # (dram__bytes_read.sum + dram__bytes_write.sum = 92.30 MB for 89.35 MB; profiles/gemv_tile_kernel_34816x5120.md),
+    # (dram__bytes_read.sum + dram__bytes_write.sum = 92.25 MB for 89.35 MB; profiles/gemv_tile_kernel_34816x5120.md),
     # scaled to the launches of one token by the bytes they process
-    traffic_ratio = 92.30 / 89.35
+    traffic_ratio = 92.25 / 89.35
     return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "traffic": traffic_ratio * total, "traffic_source": "ncu, one 34816x5120 launch, scaled by algorithmic bytes",
             "peak_source": source, "kernel": "gemv_tile_kernel (all %d decode GEMV launches of one token)" % len(jobs),
