@@ -303,6 +303,7 @@ gemv_tile_kernel(const GemvParams p) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) acc[nt][q] = acc2[nt][q] = 0.f;
 
+  uint4 bsolo[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};   // B fragments of the NT == 1 path
   int tile = blockIdx.x, done = 0, buf = 0;
   unsigned xoff = unsigned(warp) * 256;
   const unsigned xoff_step = unsigned(WS) * 256;
@@ -324,8 +325,22 @@ gemv_tile_kernel(const GemvParams p) {
           if (block_is_low(qlo)) decode_block_slow(qlo, qhi, aq, p.palette);
           if (block_is_low(rlo)) decode_block_slow(rlo, rhi, ar, p.palette);
         }
+        if (NT == 1) {
+          // One token tile: lanes whose token does not exist skip the load (their MMA columns are never
+          // stored, so whatever their registers hold is fine).  With a single token only four lanes of
+          // the warp touch shared memory: one wavefront per load instead of five.
+          if (xs_step[0]) {
+            const unsigned xa = xs_lane[0] + xoff + sub * 128;
+            bsolo[0] = lds128(xa);
+            bsolo[1] = lds128(xa + 16);
+          }
+          mma_f16(acc[0], aq[0], ar[0], aq[1], ar[1], bsolo[0].x, bsolo[0].y);
+          mma_f16(acc2[0], aq[2], ar[2], aq[3], ar[3], bsolo[0].z, bsolo[0].w);
+          mma_f16(acc[0], aq[4], ar[4], aq[5], ar[5], bsolo[1].x, bsolo[1].y);
+          mma_f16(acc2[0], aq[6], ar[6], aq[7], ar[7], bsolo[1].z, bsolo[1].w);
+        }
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
+        for (int nt = 0; nt < (NT == 1 ? 0 : NT); ++nt) {
           const unsigned xa = xs_lane[nt] + (xoff & xs_step[nt]) + sub * 128;
           const uint4 b0 = lds128(xa), b1 = lds128(xa + 16);
           mma_f16(acc[nt], aq[0], ar[0], aq[1], ar[1], b0.x, b0.y);
