@@ -107,7 +107,7 @@ int tx_set_lookahead(uint64_t handle, int lookahead);
 int tx_set_prefill(uint64_t handle, int threshold, int tile_rows);
 /* set_prefill_backend: texelator_cuda.cu:1490-1503.  0..4: streamed small-batch path in token
  * groups; 5..9: tensor-core tile candidates (rows x tokens per CTA: 128x256, 256x256, 128x128, 128x64,
- * 128x32; see tx_kernel_info). */
+ * 128x192; see tx_kernel_info). */
 int tx_set_prefill_backend(uint64_t handle, int backend);
 /* New: choose the decode path (TX_DECODE_*). TX_DECODE_TEXTURE fails with TX_EUNSUPPORTED when
  * BC4 texture views are unavailable, and with TX_ESTATE when the hardware palette differs from

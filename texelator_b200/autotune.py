@@ -9,7 +9,7 @@ facts, device facts and a hash of the kernel sources (:194-242); ``apply_profile
 profile made for another build or GPU (:247-258).
 
 The candidates are this build's sm_100a tiles of one tcgen05 kernel (output rows x tokens x columns
-per pipeline stage): 128x256x128 (baseline), 256x256x64, 128x128x128, 128x64x128, 128x32x128.  All of
+per pipeline stage): 128x256x128 (baseline), 256x256x64, 128x128x128, 128x64x128, 128x192x128.  All of
 them consume K in the same 16-column steps, so they pass the bitwise gate against each other.
 Unlike the reference, ``apply_profile`` leaves the prefill threshold alone, so single-token decode
 keeps the decode GEMV after a profile was applied.
@@ -33,7 +33,7 @@ CANDIDATES = {
     "umma_256x256x64": 6,
     "umma_128x128x128": 7,
     "umma_128x64x128": 8,
-    "umma_128x32x128": 9,
+    "umma_128x192x128": 9,
 }
 BASELINE = "umma_128x256x128"
 TOKEN_BUCKETS = (32, 128, 512, 2048, 8192, 16384, 32768, 65535)

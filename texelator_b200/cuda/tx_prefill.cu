@@ -65,10 +65,12 @@ template <int MT, int BN, int BK> struct TileConfig {
   static constexpr int fit = (220 * 1024 - fixed) / (a_stage + b_stage);
   static constexpr int stages = fit > 4 ? 4 : fit;
   static constexpr size_t smem = fixed + size_t(stages) * (a_stage + b_stage);
-  static constexpr int tmem_columns = MT * BN;
+  static constexpr int used_columns = MT * BN;
+  // allocations are powers of two (a 192-token tile takes 256 columns)
+  static constexpr int tmem_columns = used_columns <= 32 ? 32 : used_columns <= 64 ? 64 : used_columns <= 128 ? 128 : used_columns <= 256 ? 256 : 512;
   static_assert(stages >= 2, "tile does not fit two pipeline stages");
   static_assert(BN % 32 == 0, "the activation box is made of 32-token runs");
-  static_assert(tmem_columns <= 512 && (tmem_columns & (tmem_columns - 1)) == 0, "TMEM columns must be a power of two <= 512");
+  static_assert(used_columns <= 512 && BN % 16 == 0 && BN <= 256, "accumulators must fit 512 TMEM columns; N is a multiple of 16 up to 256");
 };
 
 struct PrefillParams {
@@ -394,7 +396,8 @@ static EncodeTiled encode_tiled_entry() {
 }
 
 // Tile candidates behind the reference's backend ids 5..9 (texelator/autotune.py:16-22):
-//   5: 128 rows x 256 tokens (baseline)   6: 256 x 256   7: 128 x 128   8: 128 x 64   9: 128 x 32
+//   5: 128 rows x 256 tokens (baseline)   6: 256 x 256   7: 128 x 128   8: 128 x 64   9: 128 x 192
+// (192 tokens: 5120-row matrices at 512+ tokens launch 120 CTAs instead of 80 or 160 on the 148 SMs)
 // Tall tiles re-read the activations less often (tensor-bound prompts); narrow ones suit short prompts
 // where the weight stream is the bound.
 struct TileShape {
@@ -406,7 +409,7 @@ static TileShape backend_shape(int backend) {
     case 6: return {2, 256, 64};
     case 7: return {1, 128, 128};
     case 8: return {1, 64, 128};
-    case 9: return {1, 32, 128};
+    case 9: return {1, 192, 128};
     default: return {0, 0, 0};
   }
 }
@@ -479,7 +482,7 @@ int launch_prefill_tile(const Handle *h, int backend, const __nv_bfloat16 *x, __
     case 6: return launch_tile<2, 256, 64>(h, x, y, tokens, stream);
     case 7: return launch_tile<1, 128, 128>(h, x, y, tokens, stream);
     case 8: return launch_tile<1, 64, 128>(h, x, y, tokens, stream);
-    case 9: return launch_tile<1, 32, 128>(h, x, y, tokens, stream);
+    case 9: return launch_tile<1, 192, 128>(h, x, y, tokens, stream);
     default: return fail(TX_EINVAL, "backend is not a tensor-core tile candidate");
   }
 }
@@ -510,7 +513,7 @@ int prefill_kernel_info(int backend, int64_t out[9]) {
     case 6: return tile_info<2, 256, 64>(out);
     case 7: return tile_info<1, 128, 128>(out);
     case 8: return tile_info<1, 64, 128>(out);
-    case 9: return tile_info<1, 32, 128>(out);
+    case 9: return tile_info<1, 192, 128>(out);
     default: return fail(TX_EINVAL, "backend is not a tensor-core tile candidate");
   }
 }
