@@ -198,7 +198,19 @@ class BC4Decoder:
                 self.norm2.append((1 + 0.1 * torch.randn(c.hidden, device=self.device, generator=gen)).bfloat16())
             self.final_norm = torch.ones(c.hidden, device=self.device, dtype=torch.bfloat16)
             self.embed = (torch.randn(c.vocab, c.hidden, device=self.device, generator=gen) * 0.02).bfloat16()
-            self.lm_head = (torch.randn(c.vocab, c.hidden, device=self.device, generator=gen) * 0.02).bfloat16()
+            lm_head = (torch.randn(c.vocab, c.hidden, device=self.device, generator=gen) * 0.02).bfloat16()
+            # vocabulary-parallel output head: each rank scores its slice of the vocabulary and the ranks
+            # exchange one (score, token) pair per step instead of every rank reading all 1.5 GB
+            self.vocab_parallel = tp_world > 1 and c.vocab % tp_world == 0
+            if self.vocab_parallel:
+                per = c.vocab // tp_world
+                self.vocab_offset = tp_rank * per
+                self.lm_head = lm_head[self.vocab_offset:self.vocab_offset + per].clone()
+                self.best_local = torch.zeros(2, dtype=torch.float32, device=self.device)
+                self.best_all = torch.zeros(tp_world, 2, dtype=torch.float32, device=self.device)
+            else:
+                self.lm_head = lm_head
+            del lm_head
             for h in self.handles:
                 self.ext.set_lookahead(h, lookahead)
                 self.ext.set_prefill_backend(h, prefill_backend)
@@ -324,10 +336,22 @@ class BC4Decoder:
             h = self._layer(layer, h, cos, sin, self.pos, attend, dense)
         h = _rmsnorm(h, self.final_norm, self.config.rms_eps)
         self.last_hidden.copy_(h)
-        logits = h @ self.lm_head.T
-        self.next_tok.copy_(logits.float().argmax(-1))
+        self._pick_token(h)
         self.tok.copy_(self.next_tok)
         self.pos.add_(1)
+
+    def _pick_token(self, hidden):
+        """Greedy next token from the final hidden state (bf16 output head, fp32 argmax)."""
+        logits = (hidden @ self.lm_head.T).float()
+        if not self.vocab_parallel:
+            self.next_tok.copy_(logits.argmax(-1))
+            return
+        score, index = logits.max(-1)
+        self.best_local[0:1].copy_(score)
+        self.best_local[1:2].copy_(index + self.vocab_offset)          # token ids are exact in fp32 (< 2^24)
+        torch.distributed.all_gather_into_tensor(self.best_all, self.best_local, group=self.group)
+        winner = self.best_all[:, 0].argmax().reshape(1)
+        self.next_tok.copy_(torch.index_select(self.best_all[:, 1], 0, winner).long())   # no host round trip
 
     def _add_norm(self, residual, delta, weight):
         """residual += delta (all-reduced first when it is a tensor-parallel partial); buf_x = rmsnorm(residual) * weight."""
@@ -394,8 +418,7 @@ class BC4Decoder:
             self.buf_h.copy_(residual)
         self._add_norm(self.buf_h, delta, self.final_norm)
         self.last_hidden.copy_(self.buf_x)
-        logits = self.buf_x @ self.lm_head.T
-        self.next_tok.copy_(logits.float().argmax(-1))
+        self._pick_token(self.buf_x)
         self.tok.copy_(self.next_tok)
         self.mask.index_fill_(3, self.pos, True)
         self.pos.add_(1)
