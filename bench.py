@@ -295,6 +295,11 @@ def run_gpu_arm(args, config) -> None:
         ms = timed_steps(model, steps, warmup, world, e2e=False)
     ms_e2e = timed_steps(model, steps, warmup, world, e2e=True)
     roofline = gemv_roofline(model, config, world)
+    # any bounded device wait that ran out (tcgen05 pipeline, peer exchange) leaves a code here; 0 = none
+    status = torch.tensor([model.ext.kernel_status()], device=device)
+    if world > 1:
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    kernel_status = int(status.item())
     if rank == 0:
         cpu = cpu_baseline_sample(config)
         line = {
@@ -306,6 +311,7 @@ def run_gpu_arm(args, config) -> None:
                                       "fused into the norm kernel over NVLink peer memory" if fused_allreduce else "nccl")),
             "e2e": {"value": 1000.0 / ms_e2e, "unit": UNIT, "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
             "gpu_launches": int(model.launches_per_step * steps),
+            "kernel_status": kernel_status,
             "roofline": roofline,
             "cpu_baseline": cpu,
             "clocks": clocks.summary(),
