@@ -113,6 +113,30 @@ def test_sparse_matrix_takes_low_mode_path(ext, lut):
         ext.free(h)
 
 
+@pytest.mark.parametrize("tokens", [1, 3, 40])
+def test_subnormal_numerators(ext, lut, tokens):
+    """Blocks whose endpoints are tiny: the numerators 7*e0 + g*(e1-e0) the kernels hand to the tensor
+    cores are then subnormal fp16 numbers (|n| < 4 after the 2^-16 scaling).  Flushing them would cost
+    about a third of the signal; the result has to match the un-rounded linear as closely as usual."""
+    rng = np.random.default_rng(404)
+    m, k = 64, 512
+    e0 = rng.integers(-1, 2, size=(m, k // 16))
+    e1 = e0 - 1
+    sel = rng.integers(0, 8, size=(m, k // 16, 16))
+    blocks = O.pack_blocks(e0.reshape(-1), e1.reshape(-1), sel.reshape(-1, 16)).reshape(-1)
+    scales = (rng.random(m).astype(np.float32) + 0.5)
+    x = torch.from_numpy(rng.standard_normal((tokens, k)).astype(np.float32)).bfloat16()
+    h = _pack(ext, blocks, scales)
+    try:
+        ext.set_prefill_backend(h, 5)
+        y = ext.linear(h, x.cuda()).float().cpu().numpy()
+        weights = O.dequant_weights(blocks, scales, lut, round_bf16=False).astype(np.float64)
+        ref = x.float().numpy().astype(np.float64) @ weights.T
+        assert O.rel_rms(y, ref) <= 4e-3, O.rel_rms(y, ref)
+    finally:
+        ext.free(h)
+
+
 @pytest.mark.parametrize("magnitude", [1e-30, 1e-6, 1.0, 3e4, 1e30])
 def test_activation_range(ext, lut, magnitude):
     """bf16 activations far outside the fp16 range go through the exact power-of-two rescale."""

@@ -14,14 +14,15 @@
 namespace tx {
 
 // ---------------------------------------------------------------------------------------------
-// Device layout of the BC4 payload ("tiled"): the bytes of every 8-byte block are kept verbatim
-// (only an endpoint of -128 is stored as -127, which decodes identically under BC4-SNORM), but
-// blocks are re-ordered so that one warp-wide pair of 128-bit loads fetches a 16-row x 128-column
-// unit as 1 KiB of consecutive memory:
+// Device layout of the BC4 payload ("tiled"): every block keeps its 64 bits of information (only an
+// endpoint of -128 is stored as -127, which decodes identically under BC4-SNORM), but blocks are
+// re-ordered so that one warp-wide pair of 128-bit loads fetches a 16-row x 128-column unit as 1 KiB
+// of consecutive memory, and the two blocks a lane fetches with one load are bit-shuffled into a
+// "duo" (below):
 //
 //   unit(rt, ki)  = 16 output rows [16rt, 16rt+16)  x  8 blocks [8ki, 8ki+8)      -> 1024 bytes
-//   byte offset   = (rt*KI + ki)*1024 + half*512 + lane*16 + sub*8
-//   lane = g*4+t  holds row 16rt + 8*half + g, blocks 8ki + t (sub 0) and 8ki + 4 + t (sub 1)
+//   duo offset    = (rt*KI + ki)*1024 + half*512 + lane*16
+//   lane = g*4+t  holds row 16rt + 8*half + g, blocks 8ki + t (first) and 8ki + 4 + t (second)
 //
 // This is the mma.sync m16n8k16 A-fragment ownership (lane (g,t) owns rows g and g+8), so decoded
 // weights go from registers to the tensor core with no shuffle.  Rows are padded to 16 and blocks
@@ -34,10 +35,108 @@ constexpr int kUnitBytes = 1024;
 constexpr int kPadUnits = 8;   // readable units behind the payload (unguarded prefetch of the decode GEMV)
 constexpr unsigned long long kPadBlock = 0x0000000000000001ull;  // e0=1, e1=0, selectors 0
 
-__host__ __device__ inline size_t tiled_block_offset(int row, int kb, int KI) {
+// ---------------------------------------------------------------------------------------------
+// The 16 bytes a lane loads -- blocks kb = 8ki+t ("first") and 8ki+4+t ("second") of one row -- are
+// one "duo": the same 128 bits of information as the two 8-byte blocks, re-arranged at pack time so
+// that the decode kernels need one logic instruction per pair of weights and no table:
+//
+//   word 3     the four endpoints as biased bytes u = e + 128: first e0, first e1, second e0, second e1
+//   words 0-2  for every weight the interpolation index g in place of the selector (high palette
+//              mode: selector 0,1,2..7 -> g 0,7,1..6, so that value = ((7-g)*e0 + g*e1)/7; the same
+//              bijection is applied to low-mode blocks and undone by the generic decoder).
+//              Each 16-bit half of a word holds five 3-bit fields at bits 0, 3, 6, 10, 13 and a spare
+//              bit 9; the low half carries the even position of a pair of weights, the high half the
+//              odd position, at the same offset.  A masked word is therefore an fp16x2 whose halves
+//              are the subnormal numbers g * 2^(offset-24) -- the offsets 0, 3, 6 need no shift at
+//              all, 10 and 13 share one shift by 10 -- and one HFMA2 with a per-block multiplier
+//              turns it into the exact numerators (7*e0 + g*(e1-e0)) * 2^-16 of both weights.
+//              Pairs 0-4 of the first block sit in word 0, pairs 5-7 in word 1 (offsets 0, 3, 6);
+//              pairs 0-1 of the second block in word 1 (offsets 10, 13), pairs 2-6 in word 2, and
+//              pair 7 in the three spare bits: bit k of its g values is bit 9 / bit 25 of word k.
+//
+// duo_build / duo_extract convert between this form and the canonical blocks of the file format
+// (texelator/encoder.py:105-117); every kernel that is not speed critical goes through duo_extract.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ inline unsigned selector_to_g(unsigned s) { return s == 0 ? 0u : (s == 1 ? 7u : s - 1u); }
+__host__ __device__ inline unsigned g_to_selector(unsigned g) { return g == 0 ? 0u : (g == 7 ? 1u : g + 1u); }
+
+// where pair `pair` (weights 2*pair, 2*pair+1) of block `second` lives: word index and bit offset of the
+// even weight's field (the odd weight's is 16 higher); offset -1 = the spare-bit planes
+__host__ __device__ inline void duo_slot(int second, int pair, int &word, int &offset) {
+  const int offsets[5] = {0, 3, 6, 10, 13};
+  if (!second) {
+    word = pair < 5 ? 0 : 1;
+    offset = offsets[pair < 5 ? pair : pair - 5];
+  } else if (pair < 2) {
+    word = 1;
+    offset = offsets[3 + pair];
+  } else if (pair < 7) {
+    word = 2;
+    offset = offsets[pair - 2];
+  } else {
+    word = 0;
+    offset = -1;
+  }
+}
+
+__host__ __device__ inline unsigned biased_endpoint(unsigned long long byte) {
+  unsigned u = (unsigned(byte) & 0xffu) ^ 0x80u;   // e + 128
+  return u == 0 ? 1u : u;                          // BC4-SNORM reads -128 as -127
+}
+
+__host__ __device__ inline uint4 duo_build(unsigned long long first, unsigned long long second) {
+  unsigned w[4] = {0, 0, 0, 0};
+  for (int b = 0; b < 2; ++b) {
+    const unsigned long long block = b ? second : first;
+    w[3] |= (biased_endpoint(block) | (biased_endpoint(block >> 8) << 8)) << (16 * b);
+    for (int pair = 0; pair < 8; ++pair) {
+      const unsigned even = selector_to_g(unsigned(block >> (16 + 6 * pair)) & 7u);
+      const unsigned odd = selector_to_g(unsigned(block >> (19 + 6 * pair)) & 7u);
+      int word, offset;
+      duo_slot(b, pair, word, offset);
+      if (offset >= 0) {
+        w[word] |= (even << offset) | (odd << (offset + 16));
+      } else {
+        for (int k = 0; k < 3; ++k) w[k] |= (((even >> k) & 1u) << 9) | (((odd >> k) & 1u) << 25);
+      }
+    }
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// canonical block (endpoint -128 already stored as -127) number `second` of a duo
+__host__ __device__ inline unsigned long long duo_extract(const uint4 duo, int second) {
+  const unsigned w[3] = {duo.x, duo.y, duo.z};
+  const unsigned ends = (duo.w >> (16 * second)) & 0xffffu;
+  unsigned long long block = (unsigned long long)((ends ^ 0x8080u) & 0xffffu);
+  for (int pair = 0; pair < 8; ++pair) {
+    int word, offset;
+    duo_slot(second, pair, word, offset);
+    unsigned even = 0, odd = 0;
+    if (offset >= 0) {
+      even = (w[word] >> offset) & 7u;
+      odd = (w[word] >> (offset + 16)) & 7u;
+    } else {
+      for (int k = 0; k < 3; ++k) {
+        even |= ((w[k] >> 9) & 1u) << k;
+        odd |= ((w[k] >> 25) & 1u) << k;
+      }
+    }
+    block |= (unsigned long long)g_to_selector(even) << (16 + 6 * pair);
+    block |= (unsigned long long)g_to_selector(odd) << (19 + 6 * pair);
+  }
+  return block;
+}
+
+// byte offset of the duo that holds block kb of `row`; (kb >> 2) & 1 says which of its two blocks it is
+__host__ __device__ inline size_t tiled_duo_offset(int row, int kb, int KI) {
   int rt = row >> 4, half = (row >> 3) & 1, g = row & 7;
-  int ki = kb >> 3, sub = (kb >> 2) & 1, t = kb & 3;
-  return (size_t(rt) * KI + ki) * kUnitBytes + half * 512 + (g * 4 + t) * 16 + sub * 8;
+  int ki = kb >> 3, t = kb & 3;
+  return (size_t(rt) * KI + ki) * kUnitBytes + half * 512 + (g * 4 + t) * 16;
+}
+__device__ __forceinline__ unsigned long long tiled_block(const uint8_t *tiles, int row, int kb, int KI) {
+  const uint4 duo = *reinterpret_cast<const uint4 *>(tiles + tiled_duo_offset(row, kb, KI));
+  return duo_extract(duo, (kb >> 2) & 1);
 }
 
 struct Handle {

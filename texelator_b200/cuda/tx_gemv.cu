@@ -5,16 +5,16 @@
 // the tile's 1 KiB units (16 rows x 128 columns) round-robin, keep LOOKAHEAD units in flight as
 // 128-bit loads, and turn each unit into eight mma.sync m16n8k16 A fragments entirely in registers:
 //
-//   * per block, the two int8 endpoints become fp16x2 constants  base = 7*e0, delta = e1-e0
-//     (byte-permute into the fp16 "1024+u" encoding, then one HSUB2 / HFMA2; exact integers);
-//   * per pair of 3-bit selectors, one funnel shift + one LOP3 forms the address of a
-//     lane-replicated 64-entry shared-memory table that returns the remapped interpolation
-//     indices (g(s_lo), g(s_hi)) as fp16x2 -- bank = lane, so the lookup is conflict-free;
-//   * one HFMA2 gives the exact integer numerators n = base + g*delta (|n| <= 889, exact in fp16).
+//   * the payload stores, per weight, the interpolation index g as a 3-bit field placed inside the
+//     mantissa of an fp16 half ("duo" layout, tx_common.cuh), so one AND per pair of weights yields
+//     the fp16x2 pair (g_even, g_odd) * 2^(offset-24) -- no table, no shared-memory access;
+//   * per block, the two endpoint bytes become fp16x2 constants base = 7*e0 * 2^-16 and
+//     delta * 2^(8-offset) (byte-permute into the fp16 "1024+u" encoding, HSUB2, HFMA2, three HMUL2);
+//   * one HFMA2 per pair gives the exact numerators n * 2^-16, n = 7*e0 + g*(e1-e0), |n| <= 889.
 //
 // Activations are converted once per CTA to fp16 after an exact power-of-two scaling per token
 // (so any bf16 range is safe), the tensor core accumulates n*x in fp32, and the epilogue applies
-// scale_m * 2^s / 889 and the bias before the single bf16 rounding.  The weights are therefore
+// scale_m * 2^s * 65536/889 and the bias before the single bf16 rounding.  The weights are therefore
 // never rounded to bf16: the result is the un-rounded BC4 linear, which differs from the
 // reference's bf16(pal*scale) arithmetic by that rounding only (rel-RMS about 1e-3).
 // Blocks in the low palette mode (e0 <= e1) are rare; units that contain one are flagged at pack
@@ -37,6 +37,7 @@ constexpr int kMaxTokenTiles = 4;          // 8 tokens per tile
 constexpr int kXChunks = 9;                // 8-element activation chunks a thread keeps in registers while staging
 constexpr int kXsPad = 16;                 // bytes added to the shared token stride (bank spread)
 constexpr size_t kSmemBudget = 200 * 1024; // dynamic shared memory we allow one CTA to take
+constexpr int kSmallBytes = 512;           // token multipliers, reduction words, a block of zeros
 
 struct GemvParams {
   const uint4 *tiles;
@@ -46,7 +47,7 @@ struct GemvParams {
   const __nv_bfloat16 *x;   // [T, K]
   __nv_bfloat16 *y;         // [T, M]
   const __half *xprep;      // [T, KP] pre-scaled fp16 activations (PRE) or null
-  const float *xmul;        // [T] 2^s/889 per token (PRE)
+  const float *xmul;        // [T] 2^s * 65536/889 per token (PRE)
   int M, K, KI, T, MT;
   int KP;                   // KI * 128
   int palette;              // TX_PALETTE_*
@@ -61,7 +62,7 @@ constexpr int kFuseNorm = 1;     // residual add + RMSNorm in the activation sta
 constexpr int kFuseSwiglu = 2;   // rows are (gate, up) pairs: y[t, i] = silu(gate_i) * up_i
 
 // Pre-pass for larger token counts: one CTA per token writes scaled fp16 activations and the
-// per-token multiplier 2^s/889 to scratch.
+// per-token multiplier 2^s * 65536/889 to scratch.
 __global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ xprep,
                                                                  float *__restrict__ xmul, int K, int KP) {
   __shared__ unsigned warp_max[kGemvWarps];
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const __nv_bfl
   for (int w = 0; w < kGemvWarps; ++w) m = max(m, warp_max[w]);
   float mult, inverse;
   token_scaling(m, mult, inverse);
-  if (threadIdx.x == 0) xmul[tok] = inverse * (1.0f / 889.0f);
+  if (threadIdx.x == 0) xmul[tok] = inverse * kNumeratorScale;
   uint4 *dst = reinterpret_cast<uint4 *>(xprep + size_t(tok) * KP);
   for (int i = threadIdx.x; i < padded; i += kGemvThreads)
     dst[i] = i < chunks ? convert_chunk(__ldcg(src + i), mult) : make_uint4(0, 0, 0, 0);
@@ -96,18 +97,16 @@ template <int LOOKAHEAD, int NT, bool PRE, bool LOWMODE, int FUSE = 0>
 __global__ void __launch_bounds__(kGemvThreads, (NT == 1 && LOOKAHEAD <= 2) ? 3 : (NT <= 2 ? 2 : 1))
 gemv_tile_kernel(const GemvParams p) {
   static_assert(FUSE == 0 || (NT == 1 && !PRE), "fused variants stage their activations in the CTA");
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(16) uint8_t smem_raw[];
   const unsigned sbase = unsigned(__cvta_generic_to_shared(smem_raw));
-  const unsigned lut_s = (sbase + kLutBytes - 1) & ~unsigned(kLutBytes - 1);
-  uint8_t *lut_g = smem_raw + (lut_s - sbase);
-  float *tokmul = reinterpret_cast<float *>(lut_g + kLutBytes);           // 32 floats
-  unsigned *red = reinterpret_cast<unsigned *>(lut_g + kLutBytes + 128);  // 8 words
-  uint4 *zero_g = reinterpret_cast<uint4 *>(lut_g + kLutBytes + 256);     // 256 zero bytes
-  float *part_g = reinterpret_cast<float *>(lut_g + kLutBytes + 512);     // [2][8 warps][NT*128] partial tiles
+  float *tokmul = reinterpret_cast<float *>(smem_raw);                  // 32 floats
+  unsigned *red = reinterpret_cast<unsigned *>(smem_raw + 128);         // 8 words (+ 8 floats of the fused norm)
+  uint4 *zero_g = reinterpret_cast<uint4 *>(smem_raw + 256);            // 256 zero bytes
+  float *part_g = reinterpret_cast<float *>(smem_raw + kSmallBytes);    // [2][8 warps][NT*128] partial tiles
   constexpr int kPartBytes = 2 * kGemvWarps * NT * 128 * 4;
-  uint8_t *xs_g = lut_g + kLutBytes + 512 + kPartBytes;
-  const unsigned zero_s = lut_s + kLutBytes + 256;
-  const unsigned xs_s = lut_s + kLutBytes + 512 + kPartBytes;
+  uint8_t *xs_g = smem_raw + kSmallBytes + kPartBytes;
+  const unsigned zero_s = sbase + 256;
+  const unsigned xs_s = sbase + kSmallBytes + kPartBytes;
   const unsigned xs_stride = unsigned(p.KP) * 2 + kXsPad;
 
   const int tid = threadIdx.x, lane = tid & 31;
@@ -143,7 +142,6 @@ gemv_tile_kernel(const GemvParams p) {
 #pragma unroll
   for (int i = 0; i < LOOKAHEAD; ++i) prefetch(i);
 
-  fill_pair_table(lut_g, tid, kGemvThreads, p.palette);
   if (tid < 16) zero_g[tid] = make_uint4(0, 0, 0, 0);
   // Everything above touched only the immutable payload and shared memory; the activations below are
   // produced by the previous kernel on the stream.
@@ -243,7 +241,7 @@ gemv_tile_kernel(const GemvParams p) {
       for (int w = 0; w < kGemvWarps; ++w) m = max(m, red[w]);
       float mult, inverse;
       token_scaling(m, mult, inverse);
-      if (tid == 0) tokmul[tok] = inverse * (1.0f / 889.0f);
+      if (tid == 0) tokmul[tok] = inverse * kNumeratorScale;
       uint4 *dst = reinterpret_cast<uint4 *>(xs_g + size_t(tok) * xs_stride);
 #pragma unroll
       for (int c = 0; c < kXChunks; ++c) {
@@ -258,7 +256,6 @@ gemv_tile_kernel(const GemvParams p) {
   __syncthreads();
   if (!worker || int(blockIdx.x) >= MT) return;
 
-  const unsigned lut_lane = lut_s + lane * 4;
   // shared address of this lane's activations per token tile (token = 8*nt + g); lanes whose token
   // does not exist read a block of zeros instead and never advance
   unsigned xs_lane[NT], xs_step[NT];
@@ -311,19 +308,22 @@ gemv_tile_kernel(const GemvParams p) {
   while (true) {
 #pragma unroll
     for (int slot = 0; slot < LOOKAHEAD; ++slot) {
-      const uint4 q = pend[slot][0], r = pend[slot][1];
+      const uint4 q = pend[slot][0], r = pend[slot][1];   // duos of rows g and g+8
       const unsigned flag = pflag[slot];
       // ---- one unit: blocks (ki*8 + t) [sub 0] and (ki*8 + 4 + t) [sub 1] of rows g and g+8
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
-        const unsigned qlo = sub ? q.z : q.x, qhi = sub ? q.w : q.y;
-        const unsigned rlo = sub ? r.z : r.x, rhi = sub ? r.w : r.y;
         unsigned aq[8], ar[8];
-        decode_block_fast(qlo, qhi, lut_lane, aq);
-        decode_block_fast(rlo, rhi, lut_lane, ar);
+        if (LOWMODE && p.palette == TX_PALETTE_HARDWARE) {   // uniform
+          if (sub == 0) { decode_duo_first<true>(q, aq); decode_duo_first<true>(r, ar); }
+          else { decode_duo_second<true>(q, aq); decode_duo_second<true>(r, ar); }
+        } else {
+          if (sub == 0) { decode_duo_first(q, aq); decode_duo_first(r, ar); }
+          else { decode_duo_second(q, aq); decode_duo_second(r, ar); }
+        }
         if (LOWMODE && __any_sync(0xffffffffu, flag != 0)) {   // rare, warp-uniform: redo the low-mode blocks
-          if (block_is_low(qlo)) decode_block_slow(qlo, qhi, aq, p.palette);
-          if (block_is_low(rlo)) decode_block_slow(rlo, rhi, ar, p.palette);
+          if (duo_block_is_low(q, sub)) decode_block_slow(q, sub, aq, p.palette);
+          if (duo_block_is_low(r, sub)) decode_block_slow(r, sub, ar, p.palette);
         }
         if (NT == 1) {
           // One token tile: lanes whose token does not exist skip the load (their MMA columns are never
@@ -411,7 +411,7 @@ gemv_tile_kernel(const GemvParams p) {
 // Reference-arithmetic GEMV (TX_DECODE_ALU_EXACT): w = bf16(pal*scale), fp32 FMA, one warp per
 // row (texelator_cuda.cu:141-199 without the texture unit).  Correctness path, not tuned.
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) gemv_exact_kernel(const unsigned long long *__restrict__ tiles,
+__global__ void __launch_bounds__(256) gemv_exact_kernel(const uint8_t *__restrict__ tiles,
                                                          const float *__restrict__ scales,
                                                          const __nv_bfloat16 *__restrict__ bias,
                                                          const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y,
@@ -423,7 +423,7 @@ __global__ void __launch_bounds__(256) gemv_exact_kernel(const unsigned long lon
   float scale = scales[row];
   float a0 = 0.f, a1 = 0.f;
   for (int kb = lane; kb < bpr; kb += 32) {
-    unsigned long long block = tiles[tiled_block_offset(row, kb, KI) >> 3];
+    unsigned long long block = tiled_block(tiles, row, kb, KI);
     int e0 = block_e0(block), e1 = block_e1(block);
 #pragma unroll
     for (int p = 0; p < 16; p += 2) {
@@ -442,7 +442,7 @@ int launch_gemv_exact(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y,
   for (int t0 = 0; t0 < tokens; t0 += 65535) {
     int n = std::min(tokens - t0, 65535);
     dim3 grid((h->M + 7) / 8, n);
-    gemv_exact_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const unsigned long long *>(h->tiles), h->scales, h->bias,
+    gemv_exact_kernel<<<grid, 256, 0, stream>>>(h->tiles, h->scales, h->bias,
                                                 x + size_t(t0) * h->K, y + size_t(t0) * h->M, h->M, h->K,
                                                 h->blocks_per_row, h->KI, h->palette);
     count_launch();
@@ -550,9 +550,13 @@ static GemvKernel pick_kernel(int lookahead, int nt, bool pre, bool low_mode, in
   }
 }
 
+// The lean variant decodes high-mode blocks of the software palette only; low-mode blocks and the
+// texture-unit palette's uneven interpolation weights need the variant that carries the extra code.
+static bool needs_generic_variant(const Handle *h) { return h->has_low_mode || h->palette == TX_PALETTE_HARDWARE; }
+
 static size_t gemv_smem_bytes(int KP, int tokens, int nt) {
-  // alignment slack + table, 512 bytes of small arrays, double-buffered partial tiles, activations
-  return size_t(kLutBytes) * 2 + 512 + size_t(2 * kGemvWarps * 128 * 4) * nt + size_t(tokens) * (size_t(KP) * 2 + kXsPad);
+  // small arrays, double-buffered partial tiles, activations
+  return size_t(kSmallBytes) + size_t(2 * kGemvWarps * 128 * 4) * nt + size_t(tokens) * (size_t(KP) * 2 + kXsPad);
 }
 
 static int token_tiles(int tokens) { return tokens <= 8 ? 1 : (tokens <= 16 ? 2 : 4); }
@@ -581,7 +585,7 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0) 
   // in-CTA activation conversion only while it stays a short prologue
   plan.pre = !(tokens <= 2 && size_t(tokens) * h->K <= 36864);
   if (fuse && plan.pre) return fail(TX_EINVAL, "fused linear handles at most 2 tokens with tokens * K <= 36864");
-  plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre, h->has_low_mode, fuse);
+  plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre, needs_generic_variant(h), fuse);
   plan.smem = gemv_smem_bytes(KP, tokens, plan.nt);
   // attribute + occupancy queries are cached per (device, kernel, shared bytes)
   static std::mutex guard;
@@ -738,7 +742,7 @@ int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfl
   StaticScratch *scratch = nullptr;
   int rc = static_scratch_for(h->device, &scratch);
   if (rc != TX_OK) return rc;
-  GemvKernel kernel = pick_kernel(h->lookahead, nt, true, h->has_low_mode);
+  GemvKernel kernel = pick_kernel(h->lookahead, nt, true, needs_generic_variant(h));
   TX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
   int per_sm = 0;
   TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem));

@@ -7,37 +7,42 @@
 namespace tx {
 
 // ------------------------------------------------------------------------------------------
-// retile: one thread per destination block.  Reference counterpart: the cudaMemcpy2DToArray
-// upload of texelator_cuda.cu:1296-1299 (a cudaArray is an opaque swizzled layout as well).
+// retile: one thread per destination duo (two blocks of one row, tx_common.cuh).  Reference
+// counterpart: the cudaMemcpy2DToArray upload of texelator_cuda.cu:1296-1299 (a cudaArray is an
+// opaque swizzled layout as well).
 // ------------------------------------------------------------------------------------------
-__global__ void retile_kernel(const unsigned long long *__restrict__ src, unsigned long long *__restrict__ dst,
+__global__ void retile_kernel(const unsigned long long *__restrict__ src, uint4 *__restrict__ dst,
                               uint8_t *__restrict__ unit_flags, int M, int bpr, int MT, int KI) {
-  size_t total = size_t(MT) * KI * 128;  // destination blocks
+  size_t total = size_t(MT) * KI * 64;  // destination duos
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
-    size_t unit = i >> 7;
-    int in_unit = int(i & 127);
-    int half = in_unit >> 6, lane = (in_unit >> 1) & 31, sub = in_unit & 1;
+    size_t unit = i >> 6;
+    int in_unit = int(i & 63);
+    int half = in_unit >> 5, lane = in_unit & 31;
     int rt = int(unit / KI), ki = int(unit % KI);
     int row = rt * 16 + half * 8 + (lane >> 2);
-    int kb = ki * 8 + sub * 4 + (lane & 3);
-    unsigned long long block = kPadBlock;
-    if (row < M && kb < bpr) {
-      block = src[size_t(row) * bpr + kb];
-      // BC4-SNORM reads -128 as -127; store the canonical form so the fast decoder needs no clamp
-      if ((block & 0xffull) == 0x80ull) block = (block & ~0xffull) | 0x81ull;
-      if (((block >> 8) & 0xffull) == 0x80ull) block = (block & ~0xff00ull) | 0x8100ull;
-      if (block_e0(block) <= block_e1(block)) unit_flags[unit] = 1;  // benign race: all writers store 1
+    unsigned long long blocks[2];
+#pragma unroll
+    for (int second = 0; second < 2; ++second) {
+      int kb = ki * 8 + second * 4 + (lane & 3);
+      unsigned long long block = kPadBlock;
+      if (row < M && kb < bpr) {
+        block = src[size_t(row) * bpr + kb];
+        // BC4-SNORM reads -128 as -127: compare the endpoints the decoders will see
+        int e0 = max(block_e0(block), -127), e1 = max(block_e1(block), -127);
+        if (e0 <= e1) unit_flags[unit] = 1;  // benign race: all writers store 1
+      }
+      blocks[second] = block;
     }
-    dst[i] = block;
+    dst[i] = duo_build(blocks[0], blocks[1]);
   }
 }
 
-__global__ void untile_kernel(const unsigned long long *__restrict__ tiles, unsigned long long *__restrict__ dst,
+__global__ void untile_kernel(const uint8_t *__restrict__ tiles, unsigned long long *__restrict__ dst,
                               int M, int bpr, int KI) {
   size_t total = size_t(M) * bpr;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
     int row = int(i / bpr), kb = int(i % bpr);
-    dst[i] = tiles[tiled_block_offset(row, kb, KI) >> 3];
+    dst[i] = tiled_block(tiles, row, kb, KI);
   }
 }
 
@@ -50,10 +55,10 @@ __global__ void any_flag_kernel(const uint8_t *__restrict__ flags, size_t units,
 int launch_retile(const uint8_t *rowmajor_dev, Handle *h, cudaStream_t stream) {
   size_t units = size_t(h->MT) * h->KI;
   TX_CUDA(cudaMemsetAsync(h->unit_flags, 0, units, stream));
-  size_t total = units * 128;
+  size_t total = units * 64;
   int grid = int(std::min<size_t>((total + 255) / 256, 148 * 16));
   retile_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const unsigned long long *>(rowmajor_dev),
-                                          reinterpret_cast<unsigned long long *>(h->tiles), h->unit_flags, h->M,
+                                          reinterpret_cast<uint4 *>(h->tiles), h->unit_flags, h->M,
                                           h->blocks_per_row, h->MT, h->KI);
   count_launch();
   TX_CUDA(cudaGetLastError());
@@ -73,8 +78,7 @@ int launch_retile(const uint8_t *rowmajor_dev, Handle *h, cudaStream_t stream) {
 int launch_untile(const Handle *h, uint8_t *rowmajor_dev, cudaStream_t stream) {
   size_t total = size_t(h->M) * h->blocks_per_row;
   int grid = int(std::min<size_t>((total + 255) / 256, 148 * 16));
-  untile_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const unsigned long long *>(h->tiles),
-                                          reinterpret_cast<unsigned long long *>(rowmajor_dev), h->M,
+  untile_kernel<<<grid, 256, 0, stream>>>(h->tiles, reinterpret_cast<unsigned long long *>(rowmajor_dev), h->M,
                                           h->blocks_per_row, h->KI);
   count_launch();
   TX_CUDA(cudaGetLastError());
@@ -86,12 +90,12 @@ int launch_untile(const Handle *h, uint8_t *rowmajor_dev, cudaStream_t stream) {
 // forms follow texelator_cuda.cu:141-152 (fp32 pal*scale, then one bf16 rounding).
 // ------------------------------------------------------------------------------------------
 template <int WHAT>
-__global__ void dequant_kernel(const unsigned long long *__restrict__ tiles, const float *__restrict__ scales,
+__global__ void dequant_kernel(const uint8_t *__restrict__ tiles, const float *__restrict__ scales,
                                void *__restrict__ out, int M, int bpr, int KI, int palette) {
   size_t total = size_t(M) * bpr;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
     int row = int(i / bpr), kb = int(i % bpr);
-    unsigned long long block = tiles[tiled_block_offset(row, kb, KI) >> 3];
+    unsigned long long block = tiled_block(tiles, row, kb, KI);
     int e0 = block_e0(block), e1 = block_e1(block);
     float scale = WHAT == TX_DEQUANT_PALETTE_F32 ? 1.0f : scales[row];
     float v[16];
@@ -119,7 +123,7 @@ __global__ void dequant_kernel(const unsigned long long *__restrict__ tiles, con
 int launch_dequant(const Handle *h, void *out, int what, cudaStream_t stream) {
   size_t total = size_t(h->M) * h->blocks_per_row;
   int grid = int(std::min<size_t>((total + 127) / 128, 148 * 32));
-  auto tiles = reinterpret_cast<const unsigned long long *>(h->tiles);
+  const uint8_t *tiles = h->tiles;
   switch (what) {
     case TX_DEQUANT_PALETTE_F32:
       dequant_kernel<TX_DEQUANT_PALETTE_F32><<<grid, 128, 0, stream>>>(tiles, h->scales, out, h->M, h->blocks_per_row, h->KI, h->palette);

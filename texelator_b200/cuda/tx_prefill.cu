@@ -8,14 +8,14 @@
 //   pre-pass   one small kernel rescales the activations per token by an exact power of two and stores
 //              them as fp16 (the decode GEMV's staging) in the chunk-major order of the B operand;
 //   warps 0-15 producers: 128-bit loads of the tiled BC4 payload (one 8-row half of a 16-row tile per
-//              warp), decode in registers exactly like the decode GEMV (pair table + HFMA2 -> exact
-//              integer numerators n = 7*e0 + g*(e1-e0) as fp16) and store the A tile into shared
+//              warp), decode in registers exactly like the decode GEMV (masked index fields + HFMA2 ->
+//              exact numerators n * 2^-16, n = 7*e0 + g*(e1-e0), as fp16) and store the A tile into shared
 //              memory in the canonical K-major core-matrix layout (no swizzle);
 //   warp 16    one lane issues the TMA load of the staged X tile (BN tokens x BK columns) per stage
 //              through a 3-D tensor map whose rows are 512 contiguous bytes (no multicast);
 //   warp 17    allocates TMEM, and one lane issues MT * BK/16 tcgen05.mma kind::f16 (M=128, N=BN, K=16)
 //              per stage, committing to the stage's "empty" barrier;
-//   warps 0-15 epilogue: tcgen05.ld of the fp32 accumulators, * scale_m * 2^s/889, + bias, one bf16
+//   warps 0-15 epilogue: tcgen05.ld of the fp32 accumulators, * scale_m * 2^s * 65536/889, + bias, one bf16
 //              rounding, store.
 //
 // Numerics are those of the decode GEMV: products of exact integers and exactly rescaled activations,
@@ -61,7 +61,7 @@ template <int MT, int BN, int BK> struct TileConfig {
   static constexpr int a_stage = chunks * a_lbo;
   static constexpr int b_lbo = BN * 16;
   static constexpr int b_stage = chunks * b_lbo;
-  static constexpr int fixed = 1024 /*align*/ + kLutBytes * 2 + 256 /*barriers*/;
+  static constexpr int fixed = 1024 + 16 /*alignment*/ + 256 /*barriers*/;
   static constexpr int fit = (220 * 1024 - fixed) / (a_stage + b_stage);
   static constexpr int stages = fit > 4 ? 4 : fit;
   static constexpr size_t smem = fixed + size_t(stages) * (a_stage + b_stage);
@@ -78,7 +78,7 @@ struct PrefillParams {
   const uint8_t *flags;
   const float *scales;
   const __nv_bfloat16 *bias;
-  const float *xmul;   // per-token multiplier 2^s/889 of the staged activations
+  const float *xmul;   // per-token multiplier 2^s * 65536/889 of the staged activations
   __nv_bfloat16 *y;
   int *status;
   int M, K, KI, MT, T;
@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(kStageThreads) stage_activations_kernel(const 
   const unsigned m = max(max(warp_max[4 * j], warp_max[4 * j + 1]), max(warp_max[4 * j + 2], warp_max[4 * j + 3]));
   float mult, inverse;
   token_scaling(m, mult, inverse);
-  if (threadIdx.x < 8 && tok < tokens) xmul[tok] = inverse * (1.0f / 889.0f);
+  if (threadIdx.x < 8 && tok < tokens) xmul[tok] = inverse * kNumeratorScale;
   uint4 *dst = reinterpret_cast<uint4 *>(out);
   const uint4 *src = reinterpret_cast<const uint4 *>(x + size_t(tok < tokens ? tok : 0) * K);
   for (int chunk = threadIdx.x >> 3; chunk < padded; chunk += kStageThreads / 8)
@@ -195,10 +195,8 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
   constexpr int kSubs = 128 / BK;            // pipeline stages per 128-column unit of the payload (1 or 2)
   extern __shared__ uint8_t smem_raw[];
   const unsigned sbase = unsigned(__cvta_generic_to_shared(smem_raw));
-  const unsigned lut_s = (sbase + kLutBytes - 1) & ~unsigned(kLutBytes - 1);
-  uint8_t *lut_g = smem_raw + (lut_s - sbase);
-  const unsigned bars_s = lut_s + kLutBytes;            // barriers + small state (256 bytes)
-  uint8_t *bars_g = lut_g + kLutBytes;
+  const unsigned bars_s = (sbase + 15) & ~15u;          // barriers + small state (256 bytes)
+  uint8_t *bars_g = smem_raw + (bars_s - sbase);
   const unsigned full_a = bars_s, full_b = bars_s + 8 * S, empty = bars_s + 16 * S, accum = bars_s + 24 * S;
   volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_g + 200);
   unsigned *tmem_slot = reinterpret_cast<unsigned *>(bars_g + 208);
@@ -220,7 +218,6 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  fill_pair_table(lut_g, tid, kPrefillThreads, p.palette);
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(bars_s + 208), "r"(unsigned(Cfg::tmem_columns)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -233,7 +230,6 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
   if (warp < kProducerWarps) {
     // ---------------- producers: BC4 -> fp16 A tile; warp w owns 16-row tiles w, w+8, ... of the CTA ----------------
     const int g = lane >> 2, t = lane & 3;
-    const unsigned lut_lane = lut_s + lane * 4;
     const int tile_warp = warp % kTileWarps, half0 = warp / kTileWarps;   // half0 is 0 with eight producers
     const uint4 *src[MT];
     const uint8_t *fl[MT];
@@ -285,10 +281,13 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
               if (kSubs == 2 && sub != part) continue;   // 64-column stages take one block column of the unit each
-              const unsigned lo = sub ? u.z : u.x, hi = sub ? u.w : u.y;
-              unsigned packed[8];
-              decode_block_fast(lo, hi, lut_lane, packed);          // exact integer numerators as fp16x2
-              if (cflag[m] && block_is_low(lo)) decode_block_slow(lo, hi, packed, p.palette);
+              unsigned packed[8];                                   // exact numerators n * 2^-16 as fp16x2
+              if (p.palette == TX_PALETTE_HARDWARE) {               // uniform
+                if (sub == 0) decode_duo_first<true>(u, packed); else decode_duo_second<true>(u, packed);
+              } else {
+                if (sub == 0) decode_duo_first(u, packed); else decode_duo_second(u, packed);
+              }
+              if (cflag[m] && duo_block_is_low(u, sub)) decode_block_slow(u, sub, packed, p.palette);
               // block kb of the stage -> K chunks 2kb, 2kb+1; row = (m*8 + tile_warp)*16 + half*8 + g
               const int kb = (kSubs == 2 ? 0 : sub * 4) + t;
               uint8_t *dst = stage + (2 * kb) * Cfg::a_lbo + ((m * kTileWarps + tile_warp) * 2 + half) * kASbo + g * 16;
