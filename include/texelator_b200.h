@@ -100,6 +100,35 @@ int tx_linear_static_scratch(uint64_t handle, const void *x, void *y, int tokens
 int tx_linear_fused(uint64_t handle, const void *x, const void *delta, const void *norm_weight, float eps, void *residual_out,
                     int swiglu, void *y, int tokens, int dtype, void *stream);
 
+/* No counterpart in the reference.  B200's L2 (126 MB) holds most of a decoder layer's BC4 payload, and
+ * between two weight streams the memory system idles (norms, attention, kernel boundaries).  These two
+ * calls ask it to pull bytes [offset, offset + nbytes) of a handle's packed payload (M*K/2 bytes, rows
+ * padded to 16 and columns to 128) into L2 ahead of the linear that will stream them; `offset` must be
+ * a multiple of 8192, the range is clipped to the payload.  Purely a hint: results never depend on it.
+ *   tx_prefetch                   launches a tiny kernel of its own on `stream`;
+ *   tx_prefetch_with_next_launch  attaches the request to the next kernel this thread launches through
+ *                                 tx_linear, tx_linear_fused, tx_aux_add_rmsnorm,
+ *                                 tx_aux_allreduce_add_rmsnorm or tx_aux_attention_step (its thread
+ *                                 blocks issue the prefetches as they start); nbytes = 0 cancels. */
+int tx_prefetch(uint64_t handle, size_t offset, size_t nbytes, void *stream);
+int tx_prefetch_with_next_launch(uint64_t handle, size_t offset, size_t nbytes);
+
+/* No counterpart in the reference.  One token through the single-token decode kernel with the two
+ * extras a decode loop uses (the handle must be on TX_DECODE_ALU_MMA with the software palette and no
+ * low-mode block; tx_linear_single_info tells):
+ *   x / staged       the token as bf16 [K], or in the staged form tx_aux_add_rmsnorm_single wrote for this
+ *                    K (exactly one of the two is non-NULL); results are bit-identical either way;
+ *   y / y_partial    bf16 [M] (or [M/2] with swiglu, rows paired as in tx_linear_fused), or `splits` fp32
+ *                    vectors y_partial[s * partial_stride + m]: row sums of the s-th of `splits` equal K
+ *                    ranges, scale (and, in split 0, bias) applied, not rounded.  Their sum in split order
+ *                    is the linear's output; tx_aux_add_rmsnorm_single consumes them.  K-split work items
+ *                    spread matrices with few rows over all SMs.  `splits` must divide ceil(K/128).
+ * tx_linear_single_info: out[0] = 1 if the handle qualifies, out[1] = number of splits this library
+ * would choose for it on this device, out[2] = bytes of the staged form of one token of this K. */
+int tx_linear_single(uint64_t handle, const void *x, const void *staged, int swiglu, void *y, float *y_partial, int splits,
+                     size_t partial_stride, void *stream);
+int tx_linear_single_info(uint64_t handle, int64_t out[3]);
+
 /* set_lookahead: texelator_cuda.cu:1471-1478.  k in {1,2,3,4,6,8}: 1 KiB weight requests each
  * warp keeps in flight (the reference: texture requests in flight). */
 int tx_set_lookahead(uint64_t handle, int lookahead);
@@ -168,6 +197,12 @@ int tx_kernel_status(int device, int clear);
  *                      floats; head_dim 128; long caches are walked in 64-key chunks per CTA
  *   silu_mul         : out[t,i] = silu(gate_up[t,i]) * gate_up[t,intermediate+i]                     */
 int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, int tokens, int hidden, float eps, void *stream);
+/* add_rmsnorm for one token with the extras of tx_linear_single: delta may come as `splits` fp32 partial
+ * vectors (partials[s * partial_stride + i], added in split order, rounded to bf16, then added to h), and
+ * the normalised row may also (or only: y may be NULL then) be written in staged form to `staged`
+ * (tx_linear_single_info out[2] bytes for K = hidden). */
+int tx_aux_add_rmsnorm_single(void *h, const void *delta, const float *partials, int splits, size_t partial_stride, const void *weight,
+                              void *y, void *staged, int hidden, float eps, void *stream);
 /* Tensor parallelism, one token: the all-reduce of a row-parallel linear's partial output fused into the
  * residual add + RMSNorm that consumes it.  Every rank stores `partial` [hidden] into all ranks' inboxes
  * over peer memory, publishes an epoch flag, waits (bounded; a wait that runs out records 32 in the
@@ -180,6 +215,29 @@ int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, 
 int tx_aux_allreduce_add_rmsnorm(void *h, const void *partial, const void *weight, void *y, int hidden, float eps,
                                  void *const *peer_inboxes, void *const *peer_flags, int rank, int world, void *epoch_word,
                                  void *stream);
+/* Tensor parallelism, one token, second generation of the exchange (no reference counterpart).  Every rank
+ * owns an inbox of 2 * world * (hidden / 4) 16-byte packets in peer-mapped memory (zero-initialised) and an
+ * epoch word (uint32, zero-initialised).  A packet {two bf16, epoch, two bf16, epoch} is written with one
+ * 16-byte store and is complete for a reader once both flag words show the current epoch.
+ *   tx_linear_single_push       the row-parallel linear (tx_linear_single rules; M = hidden) sends its bf16
+ *                               partial row into the inboxes of all ranks from its epilogue, tile by tile, while
+ *                               the rest of its weights still stream;
+ *   tx_aux_peer_reduce_rmsnorm  world >= 1: polls (bounded; code 32 in the status word when a poll runs out)
+ *                               the packets of all ranks in this rank's `inbox`, adds them in rank order (fp32,
+ *                               one bf16 rounding, identical bits on every rank), h += sum, y / staged =
+ *                               rmsnorm(h) * weight, and advances the epoch word.  world == 0: no exchange,
+ *                               h += delta (may be NULL): the same kernel as a multi-SM add_rmsnorm.
+ *                               Runs as one thread-block cluster of up to eight CTAs.
+ *   tx_aux_peer_best_token      vocabulary-parallel output head: every rank sends (its best score, its token +
+ *                               token_offset) to all ranks' token inboxes (2 * world packets, own epoch word);
+ *                               next_token (int64) = the token of the highest score, lowest rank on ties.
+ * All ranks must make the same sequence of calls; peer_inboxes[r] is rank r's inbox as addressable here. */
+int tx_linear_single_push(uint64_t handle, const void *x, const void *staged, void *const *peer_inboxes, int rank, int world,
+                          void *epoch_word, void *stream);
+int tx_aux_peer_reduce_rmsnorm(void *h, const void *delta, const void *weight, void *y, void *staged, int hidden, float eps,
+                               const void *inbox, int world, void *epoch_word, void *stream);
+int tx_aux_peer_best_token(const float *local_score, const void *local_token, long long token_offset, void *const *peer_inboxes, int rank,
+                           int world, void *epoch_word, void *next_token, void *stream);
 int tx_aux_rope_append(void *qkv, const float *cos_table, const float *sin_table, const void *position, void *k_cache,
                        void *v_cache, int q_heads, int kv_heads, int head_dim, int max_len, void *stream);
 int tx_aux_attention_decode(const void *qkv, const void *k_cache, const void *v_cache, const void *position, float *scratch,

@@ -71,6 +71,12 @@ def test_fused_decode_step_matches_pytorch_glue():
         for step in range(3):
             model.decode_eager(fused=True)
             assert _cosine(model.last_hidden, hidden[step]) >= 0.9995, step
+        assert model.single                      # staged activations + K-split partials (tx_linear_single)
+        model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
+        model.k_cache.copy_(state[3]); model.v_cache.copy_(state[4])
+        for step in range(3):
+            model.decode_eager(single=True)
+            assert _cosine(model.last_hidden, hidden[step]) >= 0.9995, step
         model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
         for fuse_norm, per_layer in ((False, 7), (True, 5)):
             model.fuse_norm = fuse_norm

@@ -1,6 +1,7 @@
 // C ABI of texelator_b200: handle life cycle, dispatcher, setters and info calls.
 // Reference counterparts: texelator/cuda/extension.cpp:7-48 (binding) and
 // texelator/cuda/texelator_cuda.cu:1260-1538 (implementation).
+#include <algorithm>
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
@@ -9,10 +10,12 @@
 #include <vector>
 
 #include "tx_common.cuh"
+#include "tx_decode.cuh"
 
 namespace tx {
 
 static thread_local std::string g_error;
+static thread_local PrefetchHint g_prefetch_hint;
 static std::atomic<long long> g_launches{0};
 static std::mutex g_workspace_guard;
 static std::map<int, Workspace> g_workspaces;
@@ -23,6 +26,27 @@ int fail(int code, const std::string &message) {
   return code;
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+PrefetchHint take_prefetch_hint() {
+  PrefetchHint hint = g_prefetch_hint;
+  g_prefetch_hint = PrefetchHint{};
+  return hint;
+}
+
+__global__ void prefetch_kernel(const PrefetchHint hint) {
+  grid_launch_dependents();
+  prefetch_l2_chunks(hint, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
+}
+
+// [offset, offset + nbytes) of the payload as whole chunks (the readable pad behind the payload absorbs the round-up)
+static int make_prefetch_hint(const Handle *h, size_t offset, size_t nbytes, PrefetchHint &hint) {
+  const size_t payload = size_t(h->MT) * h->KI * kUnitBytes;
+  if (offset % kPrefetchChunk) return fail(TX_EINVAL, "prefetch offset must be a multiple of 8192 bytes");
+  if (offset >= payload) return fail(TX_EINVAL, "prefetch offset lies behind the payload");
+  nbytes = std::min(nbytes, payload - offset);
+  hint.base = h->tiles + offset;
+  hint.chunks = unsigned((nbytes + kPrefetchChunk - 1) / kPrefetchChunk);
+  return TX_OK;
+}
 bool pdl_enabled() {
   static const bool enabled = [] {
     const char *value = std::getenv("TEXELATOR_B200_NO_PDL");
@@ -218,6 +242,32 @@ int tx_linear_static_scratch(uint64_t handle, const void *x, void *y, int tokens
   return rc;
 }
 
+int tx_linear_single(uint64_t handle, const void *x, const void *staged, int swiglu, void *y, float *y_partial, int splits,
+                     size_t partial_stride, void *stream_ptr) {
+  Handle *h = as_handle(handle);
+  if (!h) return fail(TX_EINVAL, "null Texelator handle");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(staged) | reinterpret_cast<uintptr_t>(y) |
+       reinterpret_cast<uintptr_t>(y_partial)) & 15)
+    return fail(TX_EINVAL, "activation and output pointers must be 16-byte aligned");
+  int current = 0;
+  TX_CUDA(cudaGetDevice(&current));
+  if (current != h->device) TX_CUDA(cudaSetDevice(h->device));
+  int rc = launch_gemv_single(h, static_cast<const __nv_bfloat16 *>(x), static_cast<const uint8_t *>(staged), swiglu != 0,
+                              static_cast<__nv_bfloat16 *>(y), y_partial, splits, partial_stride, nullptr, static_cast<cudaStream_t>(stream_ptr));
+  if (current != h->device) cudaSetDevice(current);
+  return rc;
+}
+
+int tx_linear_single_info(uint64_t handle, int64_t out[3]) {
+  Handle *h = as_handle(handle);
+  if (!h) return fail(TX_EINVAL, "null Texelator handle");
+  if (!out) return fail(TX_EINVAL, "tx_linear_single_info: null output");
+  out[0] = gemv_single_eligible(h) ? 1 : 0;
+  out[1] = gemv_suggest_splits(h);
+  out[2] = int64_t(staged_bytes(h->KI));
+  return TX_OK;
+}
+
 int tx_linear_fused(uint64_t handle, const void *x, const void *delta, const void *norm_weight, float eps, void *residual_out,
                     int swiglu, void *y, int tokens, int dtype, void *stream_ptr) {
   Handle *h = as_handle(handle);
@@ -236,6 +286,34 @@ int tx_linear_fused(uint64_t handle, const void *x, const void *delta, const voi
                              swiglu != 0, static_cast<__nv_bfloat16 *>(y), tokens, static_cast<cudaStream_t>(stream_ptr));
   if (current != h->device) cudaSetDevice(current);
   return rc;
+}
+
+int tx_prefetch_with_next_launch(uint64_t handle, size_t offset, size_t nbytes) {
+  Handle *h = as_handle(handle);
+  if (!h) return fail(TX_EINVAL, "null Texelator handle");
+  if (nbytes == 0) {
+    g_prefetch_hint = PrefetchHint{};
+    return TX_OK;
+  }
+  return make_prefetch_hint(h, offset, nbytes, g_prefetch_hint);
+}
+
+int tx_prefetch(uint64_t handle, size_t offset, size_t nbytes, void *stream_ptr) {
+  Handle *h = as_handle(handle);
+  if (!h) return fail(TX_EINVAL, "null Texelator handle");
+  if (nbytes == 0) return TX_OK;
+  PrefetchHint hint;
+  int rc = make_prefetch_hint(h, offset, nbytes, hint);
+  if (rc != TX_OK) return rc;
+  int current = 0;
+  TX_CUDA(cudaGetDevice(&current));
+  if (current != h->device) TX_CUDA(cudaSetDevice(h->device));
+  const unsigned blocks = std::min(148u, (hint.chunks + 127u) / 128u);
+  cudaError_t status = launch_pdl(prefetch_kernel, dim3(blocks), dim3(128), 0, static_cast<cudaStream_t>(stream_ptr), hint);
+  count_launch();
+  if (current != h->device) cudaSetDevice(current);
+  TX_CUDA(status);
+  return TX_OK;
 }
 
 int tx_set_lookahead(uint64_t handle, int lookahead) {

@@ -3,9 +3,12 @@
 // this to Hugging Face / PyTorch (texelator/cli.py:189-219); at batch 1 on a B200 those many small
 // PyTorch kernels cost more than the weight stream, so the decoder harness replaces them with a few
 // fused launches.  No reference counterpart; bf16 in and out, fp32 arithmetic.
+#include <cooperative_groups.h>
+
 #include <algorithm>
 
 #include "tx_common.cuh"
+#include "tx_decode.cuh"
 
 namespace tx {
 
@@ -25,9 +28,10 @@ constexpr int kNormChunks = 4;            // hidden <= 512 * 8 * 4 = 16384 stays
 
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16 *__restrict__ h, const __nv_bfloat16 *__restrict__ delta,
                                                                    const __nv_bfloat16 *__restrict__ weight, __nv_bfloat16 *__restrict__ y,
-                                                                   int hidden, float eps) {
+                                                                   int hidden, float eps, const PrefetchHint hint) {
   __shared__ float partial[kNormThreads / 32];
   grid_launch_dependents();
+  prefetch_l2_chunks(hint, blockIdx.x * kNormThreads + threadIdx.x, gridDim.x * kNormThreads);
   grid_dependency_wait();
   const int row = blockIdx.x, chunks = hidden / 8;
   uint4 *hr = reinterpret_cast<uint4 *>(h + size_t(row) * hidden);
@@ -84,6 +88,120 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16
   }
 }
 
+// The same step for one token with the two extras of the single-token decode path:
+//   * delta may arrive as `splits` fp32 partial vectors (the K ranges of a K-split linear,
+//     gemv_solo_kernel): they are added in split order and rounded to bf16 like a linear's output;
+//   * the normalised activations may also be written in the staged form the single-token decode kernel
+//     consumes (tx_decode.cuh), so that the 296 CTAs of the next linear copy 11 KB instead of each
+//     scanning, scaling and summing the row.
+struct NormExtras {
+  const float *partials;      // [splits][partial_stride] or null
+  int splits;
+  size_t partial_stride;
+  uint8_t *staged;            // staged_bytes(KI) bytes or null
+  int KI;                     // 128-column units of the consumer's rows (hidden rounded up)
+};
+
+__global__ void __launch_bounds__(kNormThreads) add_rmsnorm_single_kernel(__nv_bfloat16 *__restrict__ h, const __nv_bfloat16 *__restrict__ delta,
+                                                                          const __nv_bfloat16 *__restrict__ weight,
+                                                                          __nv_bfloat16 *__restrict__ y, int hidden, float eps,
+                                                                          const NormExtras extra, const PrefetchHint hint) {
+  __shared__ float partial[kNormThreads / 32];
+  __shared__ unsigned peak[kNormThreads / 32];
+  grid_launch_dependents();
+  prefetch_l2_chunks(hint, threadIdx.x, kNormThreads);
+  grid_dependency_wait();
+  const int chunks = hidden / 8, lane = threadIdx.x & 31;
+  uint4 *hr = reinterpret_cast<uint4 *>(h);
+  const uint4 *dr = delta ? reinterpret_cast<const uint4 *>(delta) : nullptr;
+  uint4 keep[kNormChunks];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    keep[c] = make_uint4(0, 0, 0, 0);
+    if (i < chunks) {
+      uint4 v = __ldcg(hr + i);
+      __nv_bfloat162 *pv = reinterpret_cast<__nv_bfloat162 *>(&v);
+      if (dr || extra.partials) {
+        __nv_bfloat162 d2[4];
+        if (extra.partials) {
+          float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int sp = 0; sp < extra.splits; ++sp) {
+            const float4 *src = reinterpret_cast<const float4 *>(extra.partials + size_t(sp) * extra.partial_stride) + 2 * i;
+            const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
+            sum[0] += lo.x; sum[1] += lo.y; sum[2] += lo.z; sum[3] += lo.w;
+            sum[4] += hi.x; sum[5] += hi.y; sum[6] += hi.z; sum[7] += hi.w;
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) d2[e] = __floats2bfloat162_rn(sum[2 * e], sum[2 * e + 1]);
+        } else {
+          const uint4 d = __ldcg(dr + i);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) d2[e] = reinterpret_cast<const __nv_bfloat162 *>(&d)[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 a = __bfloat1622float2(pv[e]), b = __bfloat1622float2(d2[e]);
+          pv[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+        }
+        hr[i] = v;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __bfloat1622float2(pv[e]);
+        ss += a.x * a.x + a.y * a.y;
+      }
+      keep[c] = v;
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) partial[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < kNormThreads / 32; ++w) total += partial[w];
+  const float inv = rsqrtf(total / float(hidden) + eps);
+  const uint4 *wr = reinterpret_cast<const uint4 *>(weight);
+  uint4 *yr = reinterpret_cast<uint4 *>(y);
+  unsigned m = 0;
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    if (i < chunks) {
+      uint4 v = keep[c], w = wr[i], o;
+      const __nv_bfloat162 *pv = reinterpret_cast<const __nv_bfloat162 *>(&v), *pw = reinterpret_cast<const __nv_bfloat162 *>(&w);
+      __nv_bfloat162 *po = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __bfloat1622float2(pv[e]), g = __bfloat1622float2(pw[e]);
+        po[e] = __floats2bfloat162_rn(a.x * inv * g.x, a.y * inv * g.y);
+      }
+      if (yr) yr[i] = o;
+      keep[c] = o;
+      m = max(m, chunk_absmax(o));
+    }
+  }
+  if (!extra.staged) return;
+  // ---- staged form of the normalised row (the arithmetic of gemv_solo_kernel's own staging)
+  m = __reduce_max_sync(0xffffffffu, m);
+  if (lane == 0) peak[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = 0;
+#pragma unroll
+  for (int w = 0; w < kNormThreads / 32; ++w) m = max(m, peak[w]);
+  float mult, inverse;
+  token_scaling(m, mult, inverse);
+  if (threadIdx.x == 0) *reinterpret_cast<float *>(extra.staged) = inverse * kSoloScale;
+  uint8_t *stab = extra.staged + kStagedHeader, *xs = stab + size_t(extra.KI) * 32;
+  const int padded = extra.KI * 16;
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    if (i - lane < padded) solo_stage_chunk(i, keep[c], mult, xs, stab, i < padded);   // whole warps enter
+  }
+}
+
 // ---- all-reduce fused into the residual add + RMSNorm (tensor parallelism, one token) -----------------
 // The row-parallel linears (o, down) leave a partial sum on every rank.  Instead of a collective followed
 // by the norm kernel, the norm kernel itself exchanges the partials over NVLink peer memory:
@@ -96,8 +214,6 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16
 // inbox slots suffice because a rank can only start epoch e+1 after every peer has contributed to e.
 // No multicast objects, no TMA: peer loads and stores only.  A wait that runs out records code 32 in the
 // status word and the kernel finishes with whatever the inbox holds (the host sees the status).
-constexpr int kMaxRanks = 8;
-constexpr unsigned kPeerSpinLimit = 1u << 21;
 struct PeerTable {
   uint4 *inbox[kMaxRanks];        // [2][world][hidden/8] on each rank, addressed from this rank
   unsigned *flags[kMaxRanks];     // [2][world] on each rank
@@ -108,9 +224,11 @@ __global__ void __launch_bounds__(kNormThreads) allreduce_add_rmsnorm_kernel(__n
                                                                              const __nv_bfloat16 *__restrict__ weight,
                                                                              __nv_bfloat16 *__restrict__ y, int hidden, float eps,
                                                                              PeerTable peers, int rank, int world,
-                                                                             unsigned *__restrict__ epoch_word, int *__restrict__ status) {
+                                                                             unsigned *__restrict__ epoch_word, int *__restrict__ status,
+                                                                             const PrefetchHint hint) {
   __shared__ float partial_ss[kNormThreads / 32];
   grid_launch_dependents();
+  prefetch_l2_chunks(hint, threadIdx.x, kNormThreads);
   grid_dependency_wait();
   const int chunks = hidden / 8;
   const unsigned epoch = __ldcg(epoch_word) + 1;
@@ -201,6 +319,198 @@ __global__ void __launch_bounds__(kNormThreads) allreduce_add_rmsnorm_kernel(__n
     }
   }
   if (threadIdx.x == 0) *epoch_word = epoch;
+}
+
+// ---- consumer of the packet exchange (tx_common.cuh): residual add + RMSNorm over a thread-block cluster ----
+// One cluster of up to eight CTAs; CTA c owns a contiguous range of 8-column chunks, one chunk per thread.
+// Every thread polls the two packets of its chunk from all `world` senders (all loads issued before any
+// is checked), adds them in rank order, rounds to bf16, adds the residual; the sum of squares and the
+// peak magnitude travel between the CTAs through distributed shared memory (two cluster barriers).
+// With world == 0 the delta comes from memory (or is absent) and the kernel is a multi-SM add_rmsnorm.
+constexpr int kReduceThreads = 256;
+constexpr int kReduceCluster = 8;
+
+struct ReduceParams {
+  __nv_bfloat16 *h;
+  const __nv_bfloat16 *delta;      // world == 0 only; may be null
+  const __nv_bfloat16 *weight;
+  __nv_bfloat16 *y;                // may be null when staged is given
+  uint8_t *staged;                 // staged form for tx_linear_single, or null
+  const uint4 *inbox;              // this rank's inbox
+  unsigned *epoch_word;
+  int *status;
+  int hidden, KI, world, packets;
+  float eps;
+};
+
+__global__ void __launch_bounds__(kReduceThreads) peer_reduce_rmsnorm_kernel(const ReduceParams p, const PrefetchHint hint) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float ss_all[kReduceCluster];
+  __shared__ unsigned peak_all[kReduceCluster];
+  __shared__ float ss_warp[kReduceThreads / 32];
+  __shared__ unsigned peak_warp[kReduceThreads / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ctas = int(cluster.num_blocks()), cta = int(cluster.block_rank());
+  grid_launch_dependents();
+  prefetch_l2_chunks(hint, cta * kReduceThreads + tid, ctas * kReduceThreads);
+  grid_dependency_wait();
+  const int chunks = p.hidden / 8;
+  const int per = (((chunks + ctas - 1) / ctas) + 1) & ~1;            // even: the two chunks of a block stay in one warp
+  const int i = cta * per + tid;
+  const bool live = tid < per && i < chunks;
+  const unsigned epoch = p.world ? __ldcg(p.epoch_word) + 1u : 0u;
+
+  uint4 v = make_uint4(0, 0, 0, 0);
+  float ss = 0.f;
+  if (live) {
+    v = __ldcg(reinterpret_cast<const uint4 *>(p.h) + i);
+    __nv_bfloat162 *pv = reinterpret_cast<__nv_bfloat162 *>(&v);
+    __nv_bfloat162 d2[4];
+    bool have = false;
+    if (p.world) {
+      const uint4 *base = p.inbox + (size_t(epoch & 1u) * p.world) * p.packets + 2 * i;
+      uint4 a[kMaxRanks], b[kMaxRanks];
+      unsigned pending = (1u << p.world) - 1u;
+      for (unsigned spin = 0; pending && spin < kPeerSpinLimit; ++spin) {
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (pending & (1u << r)) {
+            a[r] = load_packet(base + size_t(r) * p.packets);
+            b[r] = load_packet(base + size_t(r) * p.packets + 1);
+          }
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if ((pending & (1u << r)) && a[r].y == epoch && a[r].w == epoch && b[r].y == epoch && b[r].w == epoch) pending &= ~(1u << r);
+      }
+      if (pending && p.status) atomicCAS(p.status, 0, 32);
+      float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < p.world) {
+          const unsigned w[4] = {a[r].x, a[r].z, b[r].x, b[r].z};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            sum[2 * e] += __uint_as_float(w[e] << 16);
+            sum[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+          }
+        }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) d2[e] = __floats2bfloat162_rn(sum[2 * e], sum[2 * e + 1]);
+      have = true;
+    } else if (p.delta) {
+      const uint4 d = __ldcg(reinterpret_cast<const uint4 *>(p.delta) + i);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) d2[e] = reinterpret_cast<const __nv_bfloat162 *>(&d)[e];
+      have = true;
+    }
+    if (have) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 x = __bfloat1622float2(pv[e]), d = __bfloat1622float2(d2[e]);
+        pv[e] = __floats2bfloat162_rn(x.x + d.x, x.y + d.y);
+      }
+      reinterpret_cast<uint4 *>(p.h)[i] = v;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = __bfloat1622float2(pv[e]);
+      ss += x.x * x.x + x.y * x.y;
+    }
+  }
+  // ---- sum of squares over the cluster
+  ss = warp_sum(ss);
+  if (lane == 0) ss_warp[warp] = ss;
+  __syncthreads();
+  if (tid == 0) {
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kReduceThreads / 32; ++w) total += ss_warp[w];
+    for (int c = 0; c < ctas; ++c) cluster.map_shared_rank(ss_all, c)[cta] = total;
+  }
+  cluster.sync();
+  float total = 0.f;
+  for (int c = 0; c < ctas; ++c) total += ss_all[c];
+  const float inv = rsqrtf(total / float(p.hidden) + p.eps);
+  uint4 o = make_uint4(0, 0, 0, 0);
+  unsigned m = 0;
+  if (live) {
+    const uint4 w = reinterpret_cast<const uint4 *>(p.weight)[i];
+    const __nv_bfloat162 *pv = reinterpret_cast<const __nv_bfloat162 *>(&v), *pw = reinterpret_cast<const __nv_bfloat162 *>(&w);
+    __nv_bfloat162 *po = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = __bfloat1622float2(pv[e]), g = __bfloat1622float2(pw[e]);
+      po[e] = __floats2bfloat162_rn(x.x * inv * g.x, x.y * inv * g.y);
+    }
+    if (p.y) reinterpret_cast<uint4 *>(p.y)[i] = o;
+    m = chunk_absmax(o);
+  }
+  if (cta == 0 && tid == 0 && p.world) *p.epoch_word = epoch;     // every CTA read the word before the barrier above
+  if (!p.staged) return;
+  // ---- staged form: peak magnitude over the cluster, then the arithmetic of the linear's own staging
+  m = __reduce_max_sync(0xffffffffu, m);
+  if (lane == 0) peak_warp[warp] = m;
+  __syncthreads();
+  if (tid == 0) {
+    unsigned top = 0;
+#pragma unroll
+    for (int w = 0; w < kReduceThreads / 32; ++w) top = max(top, peak_warp[w]);
+    for (int c = 0; c < ctas; ++c) cluster.map_shared_rank(peak_all, c)[cta] = top;
+  }
+  cluster.sync();
+  m = 0;
+  for (int c = 0; c < ctas; ++c) m = max(m, peak_all[c]);
+  float mult, inverse;
+  token_scaling(m, mult, inverse);
+  if (cta == 0 && tid == 0) *reinterpret_cast<float *>(p.staged) = inverse * kSoloScale;
+  uint8_t *stab = p.staged + kStagedHeader, *xs = stab + size_t(p.KI) * 32;
+  solo_stage_chunk(i, o, mult, xs, stab, live);     // hidden is a multiple of 128 here: no padding chunks
+}
+
+// Vocabulary-parallel output head: every rank scored its slice of the vocabulary; one 16-byte packet
+// {score bits, epoch, token, epoch} per rank travels to all ranks and the best score wins (ties: lowest
+// rank, like an arg-max over the gathered list).  One warp; bounded poll.
+__global__ void __launch_bounds__(32) peer_best_token_kernel(const float *__restrict__ local_score, const long long *__restrict__ local_token,
+                                                             long long token_offset, PeerPush peers, unsigned *__restrict__ epoch_word,
+                                                             long long *__restrict__ next_token, int *__restrict__ status) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x;
+  const unsigned epoch = __ldcg(epoch_word) + 1u;
+  const size_t slot = size_t(epoch & 1u) * peers.world;
+  if (lane < peers.world)
+    store_packet(peers.inbox[lane] + slot + peers.rank, __float_as_uint(__ldcg(local_score)), unsigned(__ldcg(local_token) + token_offset), epoch);
+  float score = -INFINITY;
+  unsigned token = 0;
+  if (lane < peers.world) {
+    uint4 got = make_uint4(0, 0, 0, 0);
+    unsigned spin = 0;
+    for (; spin < kPeerSpinLimit; ++spin) {
+      got = load_packet(peers.inbox[peers.rank] + slot + lane);
+      if (got.y == epoch && got.w == epoch) break;
+    }
+    if (spin == kPeerSpinLimit && status) atomicCAS(status, 0, 32);
+    score = __uint_as_float(got.x);
+    token = got.z;
+  }
+  // arg-max with the lowest rank winning ties
+  int best = lane;
+#pragma unroll
+  for (int d = 16; d; d >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, score, d);
+    const int other_rank = __shfl_xor_sync(0xffffffffu, best, d);
+    const unsigned other_token = __shfl_xor_sync(0xffffffffu, token, d);
+    if (other > score || (other == score && other_rank < best)) {
+      score = other;
+      best = other_rank;
+      token = other_token;
+    }
+  }
+  if (lane == 0) {
+    *next_token = (long long)token;
+    *epoch_word = epoch;
+  }
 }
 
 // Rotate q and k of one token in place (rotate-half convention) and append k, v to the cache at the
@@ -416,7 +726,7 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_kernel(const _
                                                                       __nv_bfloat16 *__restrict__ k_cache,
                                                                       __nv_bfloat16 *__restrict__ v_cache, float *__restrict__ partial,
                                                                       __nv_bfloat16 *__restrict__ out, int q_heads, int kv_heads,
-                                                                      int max_len, int split_capacity, float scale) {
+                                                                      int max_len, int split_capacity, float scale, const PrefetchHint hint) {
   __shared__ __align__(16) float q_s[GROUP][kHeadDim];
   __shared__ float p_s[GROUP][kStepKeys];
   __shared__ __align__(16) float red_s[kStepThreads / 32][GROUP][kHeadDim];   // per-warp partial sums
@@ -427,6 +737,7 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_kernel(const _
   const int split = blockIdx.x, kvh = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   grid_launch_dependents();
+  prefetch_l2_chunks(hint, (blockIdx.y * gridDim.x + blockIdx.x) + gridDim.x * gridDim.y * tid, gridDim.x * gridDim.y * kStepThreads);
   grid_dependency_wait();
   const long long pos = __ldcg(position);                       // attends to keys 0..pos; key pos is new
   const int live = int(pos / kStepKeys) + 1;                    // splits that hold at least one key
@@ -635,7 +946,7 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_loop_kernel(co
                                                                       __nv_bfloat16 *__restrict__ k_cache,
                                                                       __nv_bfloat16 *__restrict__ v_cache, float *__restrict__ partial,
                                                                       __nv_bfloat16 *__restrict__ out, int q_heads, int kv_heads,
-                                                                      int max_len, int split_capacity, float scale) {
+                                                                      int max_len, int split_capacity, float scale, const PrefetchHint hint) {
   __shared__ __align__(16) float q_s[GROUP][kHeadDim];
   __shared__ float p_s[GROUP][kStepKeys];
   __shared__ __align__(16) float red_s[kStepThreads / 32][GROUP][kHeadDim];   // per-warp partial sums
@@ -652,6 +963,7 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_loop_kernel(co
   const int chunks = int(pos / kStepKeys) + 1;                  // 64-key chunks that hold at least one key
   const int splits = gridDim.x;                                 // CTA `split` takes chunks split, split + splits, ...
   const int live = min(splits, chunks);                         // CTAs with work
+  prefetch_l2_chunks(hint, (blockIdx.y * gridDim.x + blockIdx.x) + gridDim.x * gridDim.y * tid, gridDim.x * gridDim.y * kStepThreads);
   if (split >= live) return;
   const size_t q_rows = size_t(q_heads) * kHeadDim, kv_rows = size_t(kv_heads) * kHeadDim;
 
@@ -898,11 +1210,12 @@ template <int GROUP, bool LOOP>
 static cudaError_t launch_attention_step(int splits, int kv_heads, cudaStream_t s, const __nv_bfloat16 *qkv, const float *cos_table,
                                          const float *sin_table, const long long *position, __nv_bfloat16 *k_cache,
                                          __nv_bfloat16 *v_cache, float *scratch, __nv_bfloat16 *out, int q_heads, int max_len, float scale) {
+  const PrefetchHint hint = take_prefetch_hint();
   if (LOOP)
     return launch_pdl(attention_step_loop_kernel<GROUP>, dim3(splits, kv_heads), dim3(kStepThreads), 0, s, qkv, cos_table, sin_table, position,
-                      k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale);
+                      k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale, hint);
   return launch_pdl(attention_step_kernel<GROUP>, dim3(splits, kv_heads), dim3(kStepThreads), 0, s, qkv, cos_table, sin_table, position,
-                    k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale);
+                    k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale, hint);
 }
 
 }  // namespace tx
@@ -916,7 +1229,28 @@ int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, 
     return fail(TX_EINVAL, "tx_aux_add_rmsnorm: hidden must be a multiple of 8 and at most 16384");
   TX_CUDA(launch_pdl(add_rmsnorm_kernel, dim3(tokens), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
                      static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(delta),
-                     static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps));
+                     static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps, take_prefetch_hint()));
+  count_launch();
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
+int tx_aux_add_rmsnorm_single(void *h, const void *delta, const float *partials, int splits, size_t partial_stride, const void *weight,
+                              void *y, void *staged, int hidden, float eps, void *stream) {
+  if (!h || !weight || (!y && !staged) || hidden < 8 || hidden % 8 || hidden > kNormThreads * 8 * kNormChunks)
+    return fail(TX_EINVAL, "tx_aux_add_rmsnorm_single: hidden must be a multiple of 8 and at most 16384; y or staged must be given");
+  if (delta && partials) return fail(TX_EINVAL, "tx_aux_add_rmsnorm_single: pass delta or partials, not both");
+  if (partials && (splits < 1 || partial_stride < size_t(hidden) || (reinterpret_cast<uintptr_t>(partials) & 15) || partial_stride % 4))
+    return fail(TX_EINVAL, "tx_aux_add_rmsnorm_single: partials need splits >= 1, a 16-byte aligned base and a stride >= hidden that is a multiple of 4");
+  NormExtras extra{};
+  extra.partials = partials;
+  extra.splits = splits;
+  extra.partial_stride = partial_stride;
+  extra.staged = static_cast<uint8_t *>(staged);
+  extra.KI = (hidden + 127) / 128;
+  TX_CUDA(launch_pdl(add_rmsnorm_single_kernel, dim3(1), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
+                     static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(delta),
+                     static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps, extra, take_prefetch_hint()));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;
@@ -943,10 +1277,108 @@ int tx_aux_allreduce_add_rmsnorm(void *h, const void *partial, const void *weigh
   TX_CUDA(launch_pdl(allreduce_add_rmsnorm_kernel, dim3(1), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
                      static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(partial),
                      static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps, table, rank, world,
-                     static_cast<unsigned *>(epoch_word), ws ? ws->status : nullptr));
+                     static_cast<unsigned *>(epoch_word), ws ? ws->status : nullptr, take_prefetch_hint()));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;
+}
+
+static int peer_table(void *const *peer_inboxes, int rank, int world, int packets, void *epoch_word, PeerPush &out) {
+  if (!peer_inboxes || !epoch_word || world < 1 || world > kMaxRanks || rank < 0 || rank >= world)
+    return fail(TX_EINVAL, "peer exchange: world must be 1..8, rank inside it, inboxes and epoch word non-null");
+  out = PeerPush{};
+  for (int p = 0; p < world; ++p) {
+    if (!peer_inboxes[p] || (reinterpret_cast<uintptr_t>(peer_inboxes[p]) & 15)) return fail(TX_EINVAL, "peer exchange: null or unaligned inbox");
+    out.inbox[p] = static_cast<uint4 *>(peer_inboxes[p]);
+  }
+  out.epoch_word = static_cast<const unsigned *>(epoch_word);
+  out.rank = rank;
+  out.world = world;
+  out.packets = packets;
+  return TX_OK;
+}
+
+int tx_aux_peer_reduce_rmsnorm(void *h, const void *delta, const void *weight, void *y, void *staged, int hidden, float eps,
+                               const void *inbox, int world, void *epoch_word, void *stream) {
+  if (!h || !weight || (!y && !staged) || hidden < 8 || hidden % 8 || hidden > kReduceThreads * 8 * kReduceCluster)
+    return fail(TX_EINVAL, "tx_aux_peer_reduce_rmsnorm: hidden must be a multiple of 8 and at most 16384; y or staged must be given");
+  if (staged && hidden % 128) return fail(TX_EINVAL, "tx_aux_peer_reduce_rmsnorm: the staged form needs hidden to be a multiple of 128");
+  if (world < 0 || world > kMaxRanks || (world > 0 && (!inbox || !epoch_word || delta || hidden % 4)))
+    return fail(TX_EINVAL, "tx_aux_peer_reduce_rmsnorm: with world >= 1 pass the inbox and the epoch word and no delta");
+  int device = 0;
+  TX_CUDA(cudaGetDevice(&device));
+  Workspace *ws = workspace_for(device);
+  if (!ws) return TX_ECUDA;
+  ReduceParams p{};
+  p.h = static_cast<__nv_bfloat16 *>(h);
+  p.delta = static_cast<const __nv_bfloat16 *>(delta);
+  p.weight = static_cast<const __nv_bfloat16 *>(weight);
+  p.y = static_cast<__nv_bfloat16 *>(y);
+  p.staged = static_cast<uint8_t *>(staged);
+  p.inbox = static_cast<const uint4 *>(inbox);
+  p.epoch_word = static_cast<unsigned *>(epoch_word);
+  p.status = ws->status;
+  p.hidden = hidden;
+  p.KI = (hidden + 127) / 128;
+  p.world = world;
+  p.packets = hidden / 4;
+  p.eps = eps;
+  // as many CTAs as keep every thread of the cluster busy, at most eight
+  int ctas = 1;
+  while (ctas < kReduceCluster && hidden / 8 > ctas * kReduceThreads / 2) ctas *= 2;
+  if ((hidden / 8 + ctas - 1) / ctas + 1 > kReduceThreads) ctas = kReduceCluster;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(ctas);
+  config.blockDim = dim3(kReduceThreads);
+  config.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attributes[2]{};
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = ctas;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = pdl_enabled() ? 2 : 1;
+  TX_CUDA(cudaLaunchKernelEx(&config, peer_reduce_rmsnorm_kernel, p, take_prefetch_hint()));
+  count_launch();
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
+int tx_aux_peer_best_token(const float *local_score, const void *local_token, long long token_offset, void *const *peer_inboxes, int rank,
+                           int world, void *epoch_word, void *next_token, void *stream) {
+  if (!local_score || !local_token || !next_token) return fail(TX_EINVAL, "tx_aux_peer_best_token: null argument");
+  PeerPush peers;
+  int rc = peer_table(peer_inboxes, rank, world, 1, epoch_word, peers);
+  if (rc != TX_OK) return rc;
+  int device = 0;
+  TX_CUDA(cudaGetDevice(&device));
+  Workspace *ws = workspace_for(device);
+  TX_CUDA(launch_pdl(peer_best_token_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), local_score,
+                     static_cast<const long long *>(local_token), token_offset, peers, static_cast<unsigned *>(epoch_word),
+                     static_cast<long long *>(next_token), ws ? ws->status : nullptr));
+  count_launch();
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
+int tx_linear_single_push(uint64_t handle, const void *x, const void *staged, void *const *peer_inboxes, int rank, int world,
+                          void *epoch_word, void *stream) {
+  Handle *h = reinterpret_cast<Handle *>(handle);
+  if (!h || h->magic != 0x54584234) return fail(TX_EINVAL, "null Texelator handle");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(staged)) & 15)
+    return fail(TX_EINVAL, "activation pointers must be 16-byte aligned");
+  PeerPush peers;
+  int rc = peer_table(peer_inboxes, rank, world, h->M / 4, epoch_word, peers);
+  if (rc != TX_OK) return rc;
+  int current = 0;
+  TX_CUDA(cudaGetDevice(&current));
+  if (current != h->device) TX_CUDA(cudaSetDevice(h->device));
+  rc = launch_gemv_single(h, static_cast<const __nv_bfloat16 *>(x), static_cast<const uint8_t *>(staged), false, nullptr, nullptr, 1, 0,
+                          &peers, static_cast<cudaStream_t>(stream));
+  if (current != h->device) cudaSetDevice(current);
+  return rc;
 }
 
 int tx_aux_rope_append(void *qkv, const float *cos_table, const float *sin_table, const void *position, void *k_cache,

@@ -167,6 +167,43 @@ struct Workspace {
   int sm_count = 0;
 };
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-parallel exchange of one token's partial row (row-parallel linears: o, down).  Every rank owns
+// an inbox in peer-mapped memory, [2 slots][world senders][hidden / 4 packets] of 16 bytes.  A packet is
+// {two bf16, epoch, two bf16, epoch}: it is written with ONE 16-byte store, and a reader that sees the
+// current epoch in both flag words has the four values -- no fence, no separate flag, one NVLink
+// latency.  The linear's epilogue writes its packets into the inboxes of all ranks (its own included) as
+// its row tiles finish, so the transfer overlaps the rest of the weight stream; the residual add +
+// RMSNorm kernel that consumes the sum polls the packets, adds them in rank order (fp32, one bf16
+// rounding: every rank gets the same bits) and advances the epoch word.  Slots alternate with the
+// epoch; a rank can be at most one exchange ahead of a peer, so two suffice.  Every poll is bounded and
+// records code 32 in the device status word when it runs out.
+// ---------------------------------------------------------------------------------------------
+constexpr int kMaxRanks = 8;
+constexpr unsigned kPeerSpinLimit = 1u << 21;
+struct PeerPush {
+  uint4 *inbox[kMaxRanks];        // every rank's inbox as addressable from this rank
+  const unsigned *epoch_word;     // this rank's epoch counter (the consumer kernel advances it)
+  int rank, world, packets;       // packets per sender = hidden / 4
+};
+__device__ __forceinline__ void store_packet(uint4 *dst, unsigned lo, unsigned hi, unsigned epoch) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(lo), "r"(epoch), "r"(hi), "r"(epoch) : "memory");
+}
+__device__ __forceinline__ uint4 load_packet(const uint4 *src) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+  return v;
+}
+
+// A pending request "bring these bytes of a payload into L2": set by tx_prefetch_with_next_launch on
+// the calling thread, taken (and cleared) by the next kernel launch of this library on that thread.
+struct PrefetchHint {
+  const uint8_t *base = nullptr;
+  unsigned chunks = 0;           // kPrefetchChunk-byte pieces
+};
+constexpr unsigned kPrefetchChunk = 8192;
+PrefetchHint take_prefetch_hint();
+
 void set_error(const std::string &message);
 int fail(int code, const std::string &message);
 Workspace *workspace_for(int device);  // allocates on first use (never inside a launch path)
@@ -268,6 +305,20 @@ __device__ __forceinline__ float palette_value_of(int palette, int e0, int e1, i
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// L2 prefetch of payload bytes that a later kernel will stream (the 126 MB L2 holds most of a layer).
+// Fire and forget: cp.async.bulk.prefetch.L2 has no completion to wait for.  Thread `first` of `stride`
+// takes chunks first, first + stride, ...
+__device__ __forceinline__ void prefetch_l2_chunks(const PrefetchHint hint, unsigned first, unsigned stride) {
+  for (unsigned c = first; c < hint.chunks; c += stride) {
+#ifdef TX_PREFETCH_LINES
+    for (unsigned line = 0; line < kPrefetchChunk / 128; ++line)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(hint.base + size_t(c) * kPrefetchChunk + line * 128) : "memory");
+#else
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(hint.base + size_t(c) * kPrefetchChunk), "r"(kPrefetchChunk) : "memory");
+#endif
+  }
+}
+
 bool pdl_enabled();
 
 template <typename... KernelArgs, typename... Args>
@@ -292,6 +343,10 @@ int launch_dequant(const Handle *h, void *out, int what, cudaStream_t stream);
 int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_gemv_fused(const Handle *h, const __nv_bfloat16 *x, const __nv_bfloat16 *delta, const __nv_bfloat16 *gamma, float eps,
                       __nv_bfloat16 *residual_out, bool swiglu, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
+bool gemv_single_eligible(const Handle *h);
+int gemv_suggest_splits(const Handle *h);
+int launch_gemv_single(const Handle *h, const __nv_bfloat16 *x, const uint8_t *staged, bool swiglu, __nv_bfloat16 *y,
+                       float *y_partial, int splits, size_t partial_stride, const PeerPush *push, cudaStream_t stream);
 int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_gemv_exact(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_gemv_texture(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);

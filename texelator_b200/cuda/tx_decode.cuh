@@ -10,10 +10,17 @@ __device__ __forceinline__ uint4 lds128(unsigned addr) {
   asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
+// Weight loads: read once, so they bypass L1 and are marked evict-first in L2 -- lines that were
+// prefetched for a later kernel (prefetch_l2_chunks) then outlive the stream passing through.
+__device__ __forceinline__ unsigned long long stream_policy() {
+  unsigned long long policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ uint4 ldg_stream(const uint4 *p, unsigned long long policy) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.b32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
   return v;
 }
 __device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -208,6 +215,57 @@ __device__ __forceinline__ uint4 convert_chunk(uint4 c, float mult) {
     o[i] = *reinterpret_cast<unsigned *>(&h);
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Staged form of one token for the single-token decode kernel (gemv_solo_kernel): a 16-byte slot with
+// the fp32 multiplier 2^s * 2^24/889, then per 128-column unit and lane quad t the four fp16 values
+// (hi_t, hi_{t+4}, lo_t, lo_{t+4}) of 7 * S_block * 2^-24 (32 bytes per unit), then the activations as
+// fp16 with the factor 2^-offset of the index field they meet (256 bytes per unit).  The kernel stages
+// a bf16 token itself, or copies this form when the producer of the activations wrote it.
+// ---------------------------------------------------------------------------------------------
+constexpr int kStagedHeader = 16;
+__host__ __device__ inline size_t staged_bytes(int KI) { return kStagedHeader + size_t(KI) * (32 + 256); }
+constexpr float kSoloScale = 16777216.0f / 889.0f;   // sums are (n * x) * 2^-24, palette value = n / 889
+
+// exponent of the staging factor 2^-e for pair i of the first / second block of a duo (tx_common.cuh)
+__device__ __forceinline__ int solo_pair_exponent(int second, int pair) {
+  // first: offsets 0,3,6,10->0,13->3 (word 0), 0,3,6 (word 1); second: 10->0,13->3 (word 1), 0,3,6,0,3 (word 2), spare bit 9
+  const unsigned table = second ? 0x93063030u : 0x63030630u;       // nibble i = exponent of pair i
+  return int((table >> (4 * pair)) & 15u);
+}
+
+// Stages one token for gemv_solo_kernel: xs[column] = fp16(x * mult * 2^-e(column)), and per unit and
+// lane quad t the four fp16 values (hi_t, hi_{t+4}, lo_t, lo_{t+4}) of 7 * S_block * 2^-24.
+// `i` is the 8-column chunk index; chunks 2b and 2b+1 of block b sit in neighbouring lanes.
+__device__ __forceinline__ void solo_stage_chunk(int i, uint4 raw, float mult, uint8_t *xs_g, uint8_t *stab_g, bool inside) {
+  const int pair0 = 4 * (i & 1), second = (i >> 3) & 1;            // block b = i >> 1, second half of the unit when b & 4
+  unsigned w[4] = {raw.x, raw.y, raw.z, raw.w}, o[4];
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = solo_pair_exponent(second, pair0 + j);
+    const float down = __int_as_float((127 - e) << 23), up = __int_as_float((127 + e) << 23);
+    const float lo = __uint_as_float(w[j] << 16) * mult * down;
+    const float hi = __uint_as_float(w[j] & 0xffff0000u) * mult * down;
+    const __half2 h = __floats2half2_rn(lo, hi);
+    o[j] = *reinterpret_cast<const unsigned *>(&h);
+    const float2 back = __half22float2(h);                          // the value the tensor core will see
+    sum += (back.x + back.y) * up;
+  }
+  sum += __shfl_xor_sync(0xffffffffu, sum, 1);                      // both chunks of the block
+  if (inside) {
+    reinterpret_cast<uint4 *>(xs_g)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    if ((i & 1) == 0) {
+      const int block = i >> 1, unit = block >> 3, t = block & 3, high = (block >> 2) & 1;
+      const float v = sum * (7.0f / 16777216.0f);
+      const __half hi = __float2half_rn(v);
+      const __half lo = __float2half_rn(v - __half2float(hi));
+      __half *entry = reinterpret_cast<__half *>(stab_g + size_t(unit) * 32 + t * 8);
+      entry[high] = hi;
+      entry[2 + high] = lo;
+    }
+  }
 }
 
 }  // namespace tx

@@ -56,6 +56,13 @@ struct GemvParams {
   const __nv_bfloat16 *gamma;   // [K]
   __nv_bfloat16 *residual_out;  // [T, K] or null: receives bf16(x + delta); must not alias x
   float eps;
+  PrefetchHint prefetch;        // payload bytes of a later linear to pull into L2 while this one runs
+  // single-token kernel only
+  const uint8_t *staged;        // the token in staged form (tx_decode.cuh) or null: stage p.x in the kernel
+  float *y_partial;             // [splits][partial_stride] fp32 row sums of the K ranges, or null: bf16 to y
+  size_t partial_stride;
+  int splits;                   // K ranges per row tile (divides KI); 1 unless y_partial is used
+  PeerPush push;                // world > 0: the bf16 result goes as packets into every rank's inbox
 };
 
 constexpr int kFuseNorm = 1;     // residual add + RMSNorm in the activation staging
@@ -128,11 +135,12 @@ gemv_tile_kernel(const GemvParams p) {
   int pcount = 0;
   uint4 pend[LOOKAHEAD][2];
   unsigned pflag[LOOKAHEAD];
+  const unsigned long long policy = stream_policy();
   auto prefetch = [&](int slot) {
     if (unext < unit_limit) {                  // (one shared padding unit would be a hot spot for every warp's tail)
       const uint4 *src = p.tiles + size_t(unext) * 64 + lane;
-      pend[slot][0] = ldg_stream(src);
-      pend[slot][1] = ldg_stream(src + 32);
+      pend[slot][0] = ldg_stream(src, policy);
+      pend[slot][1] = ldg_stream(src + 32, policy);
       if (LOWMODE) pflag[slot] = p.flags[unext];
     }
     const bool wrap = pcount == per_tile - 1;
@@ -141,6 +149,7 @@ gemv_tile_kernel(const GemvParams p) {
   };
 #pragma unroll
   for (int i = 0; i < LOOKAHEAD; ++i) prefetch(i);
+  prefetch_l2_chunks(p.prefetch, blockIdx.x + gridDim.x * tid, gridDim.x * kGemvThreads);
 
   if (tid < 16) zero_g[tid] = make_uint4(0, 0, 0, 0);
   // Everything above touched only the immutable payload and shared memory; the activations below are
@@ -408,6 +417,284 @@ gemv_tile_kernel(const GemvParams p) {
 }
 
 // ------------------------------------------------------------------------------------------
+// Single-token decode GEMV (tokens == 1, software palette, no low-mode block): the same walk over the
+// payload as gemv_tile_kernel, but the per-weight HFMA2 is gone.  With one token seven of the eight
+// MMA columns are idle, so they are used to keep the eight blocks of a unit apart:
+//
+//   * A operand = the masked index fields themselves (one AND per pair of weights): fp16x2 subnormals
+//     g * 2^(offset-24).  K slots (2t, 2t+1) of MMA i carry pair i of the lane's first block (block t
+//     of the unit), slots (2t+8, 2t+9) pair i of its second block (block t+4).
+//   * B operand: column 2t holds the activations of block t, column 2t+1 those of block t+4, zeros
+//     elsewhere -- so only the eight lanes g = 2t / g = 2t+1 ever load activations.  The activations
+//     are staged with the factor 2^-offset of the field they meet, so every product is g*x * 2^-24.
+//   * ten MMAs (pairs 0-6, pair 7 + spare-bit plane 0, planes 1 and 2; two accumulator chains,
+//     summed afterwards) leave in the C fragment of lane
+//     (g, t) the four sums G = sum_k g_k x_k of its own four blocks (rows g, g+8 x blocks t, t+4);
+//     four FFMAs add delta * G to the lane's two row accumulators.
+//   * the base term sum_b 7*e0_b * S_b (S_b = sum of the block's activations) is one more MMA per unit
+//     into a persistent accumulator: A = the endpoints e0 as exact fp16 integers, B = 7*S_b * 2^-24
+//     split into an fp16 high and low part (K slots 0-7 and 8-15), column 0 only.
+//
+// Per unit: 42 logic instructions for the fields, 4 byte-permutes and 8 half-precision operations for
+// the endpoints, 11 MMAs, 4 FFMAs -- about half the instructions of the generic kernel.  Row sums are
+// combined over the four lanes of a row by shuffles and over the warps through shared memory in warp
+// order (deterministic; independent of LOOKAHEAD and of the number of rows of the matrix).
+// ------------------------------------------------------------------------------------------
+#ifndef TX_SOLO_MIN_CTAS
+#define TX_SOLO_MIN_CTAS 2   // resident CTAs per SM the compiler must leave registers for (build-time tuning knob)
+#endif
+constexpr int kSoloSmallBytes = 256;                               // token multiplier, reduction words
+constexpr int kSoloPartBytes = 2 * kGemvWarps * 16 * 4;            // [2][8 warps][16 rows]
+
+__device__ __forceinline__ uint2 lds64(unsigned addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ unsigned hadd2_u(unsigned a, unsigned b) {
+  unsigned d;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ void mma_f16_zero(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// Work items: an item is one 16-row tile, or with p.splits > 1 the s-th of `splits` equal K ranges of
+// a tile (item = tile * splits + s).  K-split items make matrices with few row tiles (5120 rows = 320
+// tiles on 296 resident CTAs) fill the machine evenly; their fp32 row sums go to p.y_partial[s][row]
+// and whoever consumes the linear adds the `splits` vectors in split order (the residual add + RMSNorm
+// kernel does).  Units of item `it` are it * KIs .. it * KIs + KIs - 1 of the payload (KIs = KI / splits).
+template <int LOOKAHEAD, bool SWIGLU>
+__global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  const unsigned sbase = unsigned(__cvta_generic_to_shared(smem_raw));
+  float *tokmul = reinterpret_cast<float *>(smem_raw);
+  unsigned *red = reinterpret_cast<unsigned *>(smem_raw + 128);
+  float *part_g = reinterpret_cast<float *>(smem_raw + kSoloSmallBytes);          // [2][8 warps][16 rows]
+  uint8_t *stab_g = smem_raw + kSoloSmallBytes + kSoloPartBytes;                  // KI * 32 bytes
+  uint8_t *xs_g = stab_g + size_t(p.KI) * 32;                                     // KP fp16 values
+  const unsigned stab_s = sbase + kSoloSmallBytes + kSoloPartBytes;
+  const unsigned xs_s = stab_s + unsigned(p.KI) * 32;
+
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const int g = lane >> 2, t = lane & 3;
+  const int KI = p.KI, S = p.splits, KIs = KI / S, items = p.MT * S;
+  const int WS = KIs < kGemvWarps ? KIs : kGemvWarps;
+  const bool worker = warp < WS;
+  const int per_item = worker ? (KIs - warp + WS - 1) / WS : 0;
+
+  const int item_stride = gridDim.x;
+  const unsigned unit_limit = unsigned(items) * unsigned(KIs);
+  unsigned unext = unsigned(blockIdx.x) * unsigned(KIs) + unsigned(warp);
+  const unsigned step_unit = WS, step_item = unsigned(item_stride) * unsigned(KIs) - unsigned(per_item - 1) * unsigned(WS);
+  int pcount = 0;
+  uint4 pend[LOOKAHEAD][2];
+  const unsigned long long policy = stream_policy();
+  auto prefetch = [&](int slot) {
+    if (unext < unit_limit) {
+      const uint4 *src = p.tiles + size_t(unext) * 64 + lane;
+      pend[slot][0] = ldg_stream(src, policy);
+      pend[slot][1] = ldg_stream(src + 32, policy);
+    }
+    const bool wrap = pcount == per_item - 1;
+    unext += wrap ? step_item : step_unit;
+    pcount = wrap ? 0 : pcount + 1;
+  };
+#pragma unroll
+  for (int i = 0; i < LOOKAHEAD; ++i) prefetch(i);
+  prefetch_l2_chunks(p.prefetch, blockIdx.x + gridDim.x * tid, gridDim.x * kGemvThreads);
+  grid_launch_dependents();
+  grid_dependency_wait();
+
+  // -- the token -> scaled fp16 activations and block sums in shared memory
+  {
+    const int chunks = p.K / 8, padded = p.KP / 8;
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    if (p.staged) {
+      // the kernel that produced the activations wrote them in staged form (tx_decode.cuh): copy
+      const uint4 *src = reinterpret_cast<const uint4 *>(p.staged + kStagedHeader);
+      uint4 *dst = reinterpret_cast<uint4 *>(stab_g);
+      const int total = KI * 18;
+      for (int i = tid; i < total; i += kGemvThreads) dst[i] = __ldcg(src + i);
+      if (tid == 0) tokmul[0] = __ldcg(reinterpret_cast<const float *>(p.staged));
+    } else {
+      const uint4 *xp = reinterpret_cast<const uint4 *>(p.x);
+      uint4 held[kXChunks];
+      unsigned m = 0;
+#pragma unroll
+      for (int c = 0; c < kXChunks; ++c) {
+        const int i = tid + c * kGemvThreads;
+        held[c] = i < chunks ? __ldcg(xp + i) : zero4;     // L2 read: another kernel wrote these moments ago
+        m = max(m, chunk_absmax(held[c]));
+      }
+      for (int i = tid + kXChunks * kGemvThreads; i < chunks; i += kGemvThreads) m = max(m, chunk_absmax(__ldcg(xp + i)));
+      m = __reduce_max_sync(0xffffffffu, m);
+      if (lane == 0) red[warp] = m;
+      __syncthreads();
+      m = 0;
+#pragma unroll
+      for (int w = 0; w < kGemvWarps; ++w) m = max(m, red[w]);
+      float mult, inverse;
+      token_scaling(m, mult, inverse);
+      if (tid == 0) tokmul[0] = inverse * kSoloScale;
+#pragma unroll
+      for (int c = 0; c < kXChunks; ++c) {
+        const int i = tid + c * kGemvThreads;
+        if (i - lane < padded) solo_stage_chunk(i, held[c], mult, xs_g, stab_g, i < padded);   // whole warps enter
+      }
+      for (int i0 = kXChunks * kGemvThreads + (tid - lane); i0 < padded; i0 += kGemvThreads) {
+        const int i = i0 + lane;
+        solo_stage_chunk(i, i < chunks ? __ldcg(xp + i) : zero4, mult, xs_g, stab_g, i < padded);
+      }
+    }
+  }
+  __syncthreads();
+  if (!worker || int(blockIdx.x) >= items) return;
+
+  // lanes that feed the B operand: g == 2t supplies block t (column 2t), g == 2t+1 block t+4 (column 2t+1)
+  const bool feeds_first = g == 2 * t, feeds_second = g == 2 * t + 1, feeds_base = g == 0;
+  const unsigned xs_first = xs_s + t * 32, xs_second = xs_s + 128 + t * 32, stab_lane = stab_s + t * 8;
+  unsigned xb0[8], xb1[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) xb0[i] = xb1[i] = 0u;
+  uint2 sb = make_uint2(0u, 0u);
+
+  // finalising threads: tid < 16 own row tile*16 + tid (SWIGLU: tid < 8 own the pair (tid, tid + 8))
+  float row_scale = 0.f, row_bias = 0.f, up_scale = 0.f, up_bias = 0.f;
+  bool row_live = false;
+  auto load_row_constants = [&](int item) {
+    const int row = (item / S) * 16 + tid;
+    row_live = tid < (SWIGLU ? 8 : 16) && row < p.M;
+    row_scale = row_live ? p.scales[row] : 0.f;
+    row_bias = row_live && p.bias && (item % S) == 0 ? __bfloat162float(p.bias[row]) : 0.f;
+    if (SWIGLU) {
+      up_scale = row_live ? p.scales[row + 8] : 0.f;
+      up_bias = row_live && p.bias ? __bfloat162float(p.bias[row + 8]) : 0.f;
+    }
+  };
+
+  const unsigned epoch = p.push.world ? __ldcg(p.push.epoch_word) + 1u : 0u;   // after the dependency wait: the previous
+                                                                               // exchange's consumer advanced the word
+  float acc0 = 0.f, acc1 = 0.f;                    // rows g and g+8: sum over this lane's blocks of delta * G
+  float base[4] = {0.f, 0.f, 0.f, 0.f};            // base term, column 0 (lanes t == 0: base[0] row g, base[2] row g+8)
+  int item = blockIdx.x, done = 0, buf = 0;
+  unsigned unit = unsigned(item % S) * unsigned(KIs) + unsigned(warp);   // unit within the row: selects activations
+  const int workers = WS * 32;
+  load_row_constants(item);
+  while (true) {
+#pragma unroll
+    for (int slot = 0; slot < LOOKAHEAD; ++slot) {
+      const uint4 q = pend[slot][0], r = pend[slot][1];   // duos of rows g and g+8
+      // ---- activations of this unit for the lanes that feed B; block sums for the base MMA
+      const unsigned xoff = unit * 256;
+      if (feeds_first) {
+        const uint4 v0 = lds128(xs_first + xoff), v1 = lds128(xs_first + xoff + 16);
+        xb0[0] = v0.x; xb0[1] = v0.y; xb0[2] = v0.z; xb0[3] = v0.w; xb0[4] = v1.x; xb0[5] = v1.y; xb0[6] = v1.z; xb0[7] = v1.w;
+      }
+      if (feeds_second) {
+        const uint4 v0 = lds128(xs_second + xoff), v1 = lds128(xs_second + xoff + 16);
+        xb1[0] = v0.x; xb1[1] = v0.y; xb1[2] = v0.z; xb1[3] = v0.w; xb1[4] = v1.x; xb1[5] = v1.y; xb1[6] = v1.z; xb1[7] = v1.w;
+      }
+      if (feeds_base) sb = lds64(stab_lane + unit * 32);
+      const unsigned plane1 = hadd2_u(xb1[7], xb1[7]), plane2 = hadd2_u(plane1, plane1);
+      // ---- endpoints: (e0 first | e0 second) as exact fp16 integers, (delta first | delta second)
+      const unsigned q0 = __byte_perm(q.w, 0x64646464u, 0x4240), q1 = __byte_perm(q.w, 0x64646464u, 0x4341);
+      const unsigned r0 = __byte_perm(r.w, 0x64646464u, 0x4240), r1 = __byte_perm(r.w, 0x64646464u, 0x4341);
+      const unsigned e0q = hadd2_u(q0, 0xE480E480u), e0r = hadd2_u(r0, 0xE480E480u);   // - (1024 + 128)
+      const unsigned dq = hsub2_u(q1, q0), dr = hsub2_u(r1, r0);
+      mma_f16(base, e0q, e0r, e0q, e0r, sb.x, sb.y);
+      // ---- G = sum g * x per block: ten MMAs in two independent accumulator chains
+      const unsigned qs0 = q.x >> 10, qs1 = q.y >> 10, qs2 = q.z >> 10;
+      const unsigned rs0 = r.x >> 10, rs1 = r.y >> 10, rs2 = r.z >> 10;
+      float ca[4], cb[4];
+      mma_f16_zero(ca, q.x & kField0, r.x & kField0, qs1 & kField0, rs1 & kField0, xb0[0], xb1[0]);
+      mma_f16_zero(cb, q.x & kField3, r.x & kField3, qs1 & kField3, rs1 & kField3, xb0[1], xb1[1]);
+      mma_f16(ca, q.x & kField6, r.x & kField6, q.z & kField0, r.z & kField0, xb0[2], xb1[2]);
+      mma_f16(cb, qs0 & kField0, rs0 & kField0, q.z & kField3, r.z & kField3, xb0[3], xb1[3]);
+      mma_f16(ca, qs0 & kField3, rs0 & kField3, q.z & kField6, r.z & kField6, xb0[4], xb1[4]);
+      mma_f16(cb, q.y & kField0, r.y & kField0, qs2 & kField0, rs2 & kField0, xb0[5], xb1[5]);
+      mma_f16(ca, q.y & kField3, r.y & kField3, qs2 & kField3, rs2 & kField3, xb0[6], xb1[6]);
+      mma_f16(cb, q.y & kField6, r.y & kField6, q.x & kFieldSpare, r.x & kFieldSpare, xb0[7], xb1[7]);
+      mma_f16(ca, 0u, 0u, q.y & kFieldSpare, r.y & kFieldSpare, 0u, plane1);
+      mma_f16(cb, 0u, 0u, q.z & kFieldSpare, r.z & kFieldSpare, 0u, plane2);
+      const float g0 = ca[0] + cb[0], g1 = ca[1] + cb[1], g2 = ca[2] + cb[2], g3 = ca[3] + cb[3];
+      {
+        const __half2 hq = *reinterpret_cast<const __half2 *>(&dq), hr = *reinterpret_cast<const __half2 *>(&dr);
+        const float2 fq = __half22float2(hq), fr = __half22float2(hr);
+        acc0 = fmaf(fq.x, g0, acc0);
+        acc0 = fmaf(fq.y, g1, acc0);
+        acc1 = fmaf(fr.x, g2, acc1);
+        acc1 = fmaf(fr.y, g3, acc1);
+      }
+      prefetch(slot);
+      unit += unsigned(WS);
+      if (++done == per_item) {
+        // ---- this warp's share of the item is done: rows over the lane quad, then over the warps
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+        if (t == 0) {
+          float *mine = part_g + (buf * kGemvWarps + warp) * 16;
+          mine[g] = acc0 + base[0];
+          mine[g + 8] = acc1 + base[2];
+        }
+        acc0 = acc1 = 0.f;
+        base[0] = base[1] = base[2] = base[3] = 0.f;
+        asm volatile("bar.sync 1, %0;" ::"r"(workers) : "memory");
+        if (p.push.world) {
+          // tensor-parallel partial: packets of four consecutive rows into every rank's inbox (warp 0)
+          if (tid < 32) {
+            unsigned bits = 0;
+            if (row_live) {
+              const float *src = part_g + buf * kGemvWarps * 16 + tid;
+              float sum = 0.f;
+              for (int w = 0; w < WS; ++w) sum += src[w * 16];
+              bits = __bfloat16_as_ushort(__float2bfloat16(fmaf(sum, row_scale * tokmul[0], row_bias)));
+            }
+            const unsigned b1 = __shfl_down_sync(0xffffffffu, bits, 1), b2 = __shfl_down_sync(0xffffffffu, bits, 2);
+            const unsigned b3 = __shfl_down_sync(0xffffffffu, bits, 3);
+            const int row = (item / S) * 16 + tid;
+            if (tid < 16 && (tid & 3) == 0 && row < p.M) {
+              const size_t at = (size_t(epoch & 1u) * p.push.world + p.push.rank) * p.push.packets + (row >> 2);
+              for (int peer = 0; peer < p.push.world; ++peer)
+                store_packet(p.push.inbox[peer] + at, bits | (b1 << 16), b2 | (b3 << 16), epoch);
+            }
+          }
+        } else if (row_live) {
+          const float *src = part_g + buf * kGemvWarps * 16 + tid;
+          float sum = 0.f;
+          for (int w = 0; w < WS; ++w) sum += src[w * 16];
+          const float tm = tokmul[0];
+          const int tile = item / S;
+          if (SWIGLU) {
+            float up_sum = 0.f;
+            for (int w = 0; w < WS; ++w) up_sum += src[w * 16 + 8];
+            const float gate = __bfloat162float(__float2bfloat16(fmaf(sum, row_scale * tm, row_bias)));
+            const float up = __bfloat162float(__float2bfloat16(fmaf(up_sum, up_scale * tm, up_bias)));
+            p.y[tile * 8 + tid] = __float2bfloat16(gate / (1.f + __expf(-gate)) * up);
+          } else if (p.y_partial) {
+            p.y_partial[size_t(item % S) * p.partial_stride + tile * 16 + tid] = fmaf(sum, row_scale * tm, row_bias);
+          } else {
+            p.y[tile * 16 + tid] = __float2bfloat16(fmaf(sum, row_scale * tm, row_bias));
+          }
+        }
+        buf ^= 1;
+        item += item_stride;
+        if (item >= items) return;
+        done = 0;
+        unit = unsigned(item % S) * unsigned(KIs) + unsigned(warp);
+        load_row_constants(item);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // Reference-arithmetic GEMV (TX_DECODE_ALU_EXACT): w = bf16(pal*scale), fp32 FMA, one warp per
 // row (texelator_cuda.cu:141-199 without the texture unit).  Correctness path, not tuned.
 // ------------------------------------------------------------------------------------------
@@ -554,6 +841,20 @@ static GemvKernel pick_kernel(int lookahead, int nt, bool pre, bool low_mode, in
 // texture-unit palette's uneven interpolation weights need the variant that carries the extra code.
 static bool needs_generic_variant(const Handle *h) { return h->has_low_mode || h->palette == TX_PALETTE_HARDWARE; }
 
+template <bool SWIGLU>
+static GemvKernel pick_solo(int lookahead) {
+  switch (lookahead) {
+    case 1: return gemv_solo_kernel<1, SWIGLU>;
+    case 2: return gemv_solo_kernel<2, SWIGLU>;
+    case 3: return gemv_solo_kernel<3, SWIGLU>;
+    case 4: return gemv_solo_kernel<4, SWIGLU>;
+    case 6: return gemv_solo_kernel<6, SWIGLU>;
+    default: return gemv_solo_kernel<8, SWIGLU>;
+  }
+}
+
+static size_t solo_smem_bytes(int KI) { return size_t(kSoloSmallBytes) + kSoloPartBytes + size_t(KI) * 32 + size_t(KI) * 256; }
+
 static size_t gemv_smem_bytes(int KP, int tokens, int nt) {
   // small arrays, double-buffered partial tiles, activations
   return size_t(kSmallBytes) + size_t(2 * kGemvWarps * 128 * 4) * nt + size_t(tokens) * (size_t(KP) * 2 + kXsPad);
@@ -573,11 +874,11 @@ static int tokens_per_pass(int KP) {
 struct GemvPlan {
   GemvKernel kernel;
   int nt, grid;
-  bool pre;
+  bool pre, solo;
   size_t smem;
 };
 
-static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0) {
+static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, bool single_token_kernel = false) {
   Workspace *ws = workspace_for(h->device);
   if (!ws) return TX_ECUDA;
   int KP = h->KI * 128;
@@ -585,8 +886,17 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0) 
   // in-CTA activation conversion only while it stays a short prologue
   plan.pre = !(tokens <= 2 && size_t(tokens) * h->K <= 36864);
   if (fuse && plan.pre) return fail(TX_EINVAL, "fused linear handles at most 2 tokens with tokens * K <= 36864");
-  plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre, needs_generic_variant(h), fuse);
-  plan.smem = gemv_smem_bytes(KP, tokens, plan.nt);
+  // The single-token kernel (no per-weight arithmetic) is taken on request only (tx_linear_single): it
+  // pays off when its token arrives staged; staging a bf16 row costs it more than the general kernel.
+  plan.solo = single_token_kernel;
+  if (plan.solo) {
+    plan.pre = false;
+    plan.kernel = (fuse & kFuseSwiglu) ? pick_solo<true>(h->lookahead) : pick_solo<false>(h->lookahead);
+    plan.smem = solo_smem_bytes(h->KI);
+  } else {
+    plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre, needs_generic_variant(h), fuse);
+    plan.smem = gemv_smem_bytes(KP, tokens, plan.nt);
+  }
   // attribute + occupancy queries are cached per (device, kernel, shared bytes)
   static std::mutex guard;
   static std::map<std::tuple<int, const void *, size_t>, int> cache;
@@ -634,6 +944,8 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
     p.T = n;
     p.KP = KP;
     p.palette = h->palette;
+    p.splits = 1;
+    p.prefetch = take_prefetch_hint();
     if (plan.pre) {
       // scaled fp16 activations go through the per-device scratch (one pre-pass CTA per token)
       if (size_t(n) * KP > ws->xprep_halfs) return fail(TX_EINVAL, "tokens*K exceeds the activation scratch of the decode GEMV");
@@ -680,7 +992,72 @@ int launch_gemv_fused(const Handle *h, const __nv_bfloat16 *x, const __nv_bfloat
   p.gamma = gamma;
   p.residual_out = residual_out;
   p.eps = eps;
+  p.splits = 1;
+  p.prefetch = take_prefetch_hint();
   TX_CUDA(launch_pdl(plan.kernel, dim3(plan.grid), dim3(kGemvThreads), plan.smem, stream, p));
+  count_launch();
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
+bool gemv_single_eligible(const Handle *h) {
+  return h->decode_path == TX_DECODE_ALU_MMA && !needs_generic_variant(h) && solo_smem_bytes(h->KI) <= kSmemBudget;
+}
+
+// Number of K ranges for a partial-sum launch.  Two ranges help when the row tiles do not fill the resident
+// CTAs evenly (5120 rows = 320 tiles on 296 CTAs: the last 24 tiles run alone at a fraction of the
+// bandwidth); more ranges cost more in per-item combines than they gain (measured on 5120x17408:
+// 1 range 18.4 us, 2 ranges 16.7 us, 4 ranges 18.8 us).
+int gemv_suggest_splits(const Handle *h) {
+  Workspace *ws = workspace_for(h->device);
+  if (!ws || !gemv_single_eligible(h) || h->KI % 2 || h->KI < 16) return 1;
+  const int slots = ws->sm_count * 2;
+  const double one = double((h->MT + slots - 1) / slots), two = double((2 * h->MT + slots - 1) / slots) / 2.0;
+  return two < 0.85 * one ? 2 : 1;
+}
+
+// One token through the single-token kernel with its extras: the token may arrive in staged form
+// (written by the kernel that produced it), the result may leave as `splits` fp32 partial vectors.
+int launch_gemv_single(const Handle *h, const __nv_bfloat16 *x, const uint8_t *staged, bool swiglu, __nv_bfloat16 *y,
+                       float *y_partial, int splits, size_t partial_stride, const PeerPush *push, cudaStream_t stream) {
+  if (!gemv_single_eligible(h))
+    return fail(TX_EUNSUPPORTED, "the single-token kernel needs the ALU decode path, the software palette and a payload without low-mode blocks");
+  if ((x == nullptr) == (staged == nullptr)) return fail(TX_EINVAL, "pass the token either as bf16 or in staged form");
+  if (int(y != nullptr) + int(y_partial != nullptr) + int(push != nullptr) != 1)
+    return fail(TX_EINVAL, "pass either a bf16 output or a partial-sum output");
+  if (push && (swiglu || h->M % 4 || push->packets != h->M / 4 || push->world < 1 || push->world > kMaxRanks || push->rank < 0 ||
+               push->rank >= push->world || !push->epoch_word))
+    return fail(TX_EINVAL, "peer push needs M a multiple of 4, hidden / 4 packets per sender and 1..8 ranks");
+  if (swiglu && (y_partial || h->M % 16)) return fail(TX_EINVAL, "SwiGLU needs a bf16 output and M a multiple of 16");
+  if (!y_partial) splits = 1;
+  if (splits < 1 || h->KI % splits) return fail(TX_EINVAL, "splits must divide the number of 128-column units of a row");
+  if (y_partial && partial_stride < size_t(h->M)) return fail(TX_EINVAL, "partial_stride is smaller than M");
+  Workspace *ws = workspace_for(h->device);
+  if (!ws) return TX_ECUDA;
+  GemvPlan plan;
+  int rc = plan_gemv(h, 1, plan, swiglu ? kFuseSwiglu : 0, true);
+  if (rc != TX_OK) return rc;
+  GemvParams p{};
+  p.tiles = reinterpret_cast<const uint4 *>(h->tiles);
+  p.scales = h->scales;
+  p.bias = h->bias;
+  p.x = x;
+  p.y = y;
+  p.M = h->M;
+  p.K = h->K;
+  p.KI = h->KI;
+  p.MT = h->MT;
+  p.T = 1;
+  p.KP = h->KI * 128;
+  p.palette = h->palette;
+  p.staged = staged;
+  p.y_partial = y_partial;
+  p.partial_stride = partial_stride;
+  p.splits = splits;
+  if (push) p.push = *push;
+  p.prefetch = take_prefetch_hint();
+  const int grid = std::max(1, std::min(h->MT * splits, ws->sm_count * 2));
+  TX_CUDA(launch_pdl(plan.kernel, dim3(grid), dim3(kGemvThreads), plan.smem, stream, p));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;

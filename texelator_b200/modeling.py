@@ -62,6 +62,7 @@ CONFIGS = {
     "70b-class": DecoderConfig("70b-class", 8192, 80, 64, 8, 128, 28672, 128256, rope_theta=5e5),
     "toy": DecoderConfig("toy", 256, 2, 4, 2, 64, 512, 1024, qkv_bias=True),
     "toy128": DecoderConfig("toy128", 512, 3, 8, 2, 128, 1024, 2048, qkv_bias=True),
+    "toy128x8": DecoderConfig("toy128x8", 1024, 2, 16, 8, 128, 2048, 4096, qkv_bias=True),      # splits 8 ways
 }
 
 
@@ -240,6 +241,18 @@ class BC4Decoder:
                                                 self.ext.attention_step_scratch_floats(q_heads, max_len)),
                                             dtype=torch.float32, device=self.device)
             self.fused = c.head_dim == 128 and (c.q_heads // c.kv_heads) <= 8 and c.hidden <= 18432 and self.i_loc % 8 == 0
+            # single-token decode path (tx_linear_single): the norm kernels hand the qkv and gate/up linears their
+            # token in staged form, the o and down linears leave K-split fp32 partial sums that the next norm adds
+            info = [self.ext.linear_single_info(h) for h in self.handles]
+            self.single = self.fused and c.hidden <= 16384 and c.hidden % 128 == 0 and all(i[0] for i in info)
+            self.k_split = False
+            if self.single:
+                self.split_o = self.ext.linear_single_info(self.h_o[0])[1]
+                self.split_down = self.ext.linear_single_info(self.h_down[0])[1]
+                stride = (c.hidden + 31) // 32 * 32
+                self.part_o = torch.zeros(self.split_o, stride, dtype=torch.float32, device=self.device)
+                self.part_down = torch.zeros(self.split_down, stride, dtype=torch.float32, device=self.device)
+                self.staged_h = torch.zeros(self.ext.linear_single_info(self.h_qkv[0])[2], dtype=torch.uint8, device=self.device)
         # tensor parallelism: the all-reduce of the o/down partials fused into the next residual add + norm
         # over peer memory (tp.PeerExchange); None keeps the NCCL all-reduce
         self.peers = None
@@ -347,6 +360,9 @@ class BC4Decoder:
             self.next_tok.copy_(logits.argmax(-1))
             return
         score, index = logits.max(-1)
+        if self.peers is not None and self.single:
+            self.ext.peer_best_token(score.contiguous(), index.contiguous(), self.vocab_offset, self.peers, self.next_tok)
+            return
         self.best_local[0:1].copy_(score)
         self.best_local[1:2].copy_(index + self.vocab_offset)          # token ids are exact in fp32 (< 2^24)
         torch.distributed.all_gather_into_tensor(self.best_all, self.best_local, group=self.group)
@@ -378,6 +394,52 @@ class BC4Decoder:
         if int(flag.item()) == 0:
             self.peers = None
         return self.peers is not None
+
+    def _decode_step_single(self):
+        """One decode step on the single-token path, seven launches per layer.  The norm kernels write their
+        output in the staged form of ``tx_linear_single`` (the qkv and gate/up linears then copy 11 KB instead
+        of each CTA scanning and converting the row).  On one GPU the o and down linears, whose inputs come
+        from many CTAs, stage for themselves in the general decode kernel (``self.k_split`` lets them leave
+        K-split fp32 partial sums for the next norm instead).  Tensor-parallel, they push their partial rows
+        into every rank's packet inbox from their epilogue and the next norm (one thread-block cluster) polls
+        and adds the packets of all ranks; the output head exchanges one (score, token) packet per rank."""
+        c, ext = self.config, self.ext
+        q_heads, kv_heads = c.q_heads // self.world, c.kv_heads // self.world
+        peers = self.peers if self.world > 1 else None
+        torch.index_select(self.embed, 0, self.tok, out=self.buf_h)
+
+        def norm(weight, pending, **outputs):
+            if peers is not None:
+                ext.peer_reduce_rmsnorm(self.buf_h, weight, c.rms_eps, peers=peers if pending else None, **outputs)
+            else:
+                ext.add_rmsnorm_single(self.buf_h, weight, c.rms_eps, **pending, **outputs)
+
+        def row_parallel(handle, x, out, partials):
+            if peers is not None:
+                ext.linear_single_push(handle, x, peers)
+                return dict(pushed=True)
+            if self.k_split:
+                ext.linear_single(handle, x, None, partials=partials)
+                return dict(partials=partials)
+            ext.linear_out(handle, x, out)
+            return dict(delta=out)
+
+        pending = {}
+        for layer in range(c.layers):
+            norm(self.norm1[layer], pending, staged=self.staged_h)
+            ext.linear_single(self.h_qkv[layer], None, self.buf_qkv, staged=self.staged_h)
+            ext.attention_step(self.buf_qkv, self.cos, self.sin, self.pos, self.k_cache[layer], self.v_cache[layer],
+                               self.attn_scratch, self.buf_attn, q_heads, kv_heads, c.head_dim)
+            pending = row_parallel(self.h_o[layer], self.buf_attn, self.buf_o, self.part_o)
+            norm(self.norm2[layer], pending, staged=self.staged_h)
+            ext.linear_single(self.h_gu[layer], None, self.buf_act, staged=self.staged_h, swiglu=True)
+            pending = row_parallel(self.h_down[layer], self.buf_act, self.buf_down, self.part_down)
+        norm(self.final_norm, pending, y=self.buf_x)
+        self.last_hidden.copy_(self.buf_x)
+        self._pick_token(self.buf_x)
+        self.tok.copy_(self.next_tok)
+        self.mask.index_fill_(3, self.pos, True)
+        self.pos.add_(1)
 
     def _decode_step_fused(self):
         """One decode step with the library's fused kernels, five launches per layer: qkv linear (with the
@@ -424,8 +486,10 @@ class BC4Decoder:
         self.pos.add_(1)
 
     @torch.no_grad()
-    def decode_eager(self, dense: bool = False, fused: bool = False) -> None:
-        if fused:
+    def decode_eager(self, dense: bool = False, fused: bool = False, single: bool = False) -> None:
+        if single:
+            self._decode_step_single()
+        elif fused:
             self._decode_step_fused()
         else:
             self._decode_step(dense)
@@ -434,7 +498,8 @@ class BC4Decoder:
     def capture(self, fused: bool | None = None) -> None:
         """Capture one decode step (all layers, lm_head, argmax, position update) in a CUDA graph.
         ``fused`` (default: when the shapes allow) uses the library's glue kernels instead of PyTorch ops."""
-        step = self._decode_step_fused if (self.fused if fused is None else fused) else self._decode_step
+        use_fused = self.fused if fused is None else fused
+        step = self._decode_step if not use_fused else (self._decode_step_single if self.single and fused is None and not self.fuse_norm and (self.world == 1 or self.peers is not None) else self._decode_step_fused)
         stream = torch.cuda.Stream(self.device)
         saved = (self.tok.clone(), self.pos.clone(), self.mask.clone())
         with torch.cuda.stream(stream):

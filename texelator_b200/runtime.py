@@ -70,6 +70,14 @@ C_API = {
     "tx_aux_attention_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp]),
     "tx_aux_silu_mul": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "tx_launch_count": (ctypes.c_int64, []),
+    "tx_linear_single": (_i32, [_u64, _vp, _vp, _i32, _vp, _vp, _i32, ctypes.c_size_t, _vp]),
+    "tx_linear_single_info": (_i32, [_u64, _vp]),
+    "tx_aux_add_rmsnorm_single": (_i32, [_vp, _vp, _vp, _i32, ctypes.c_size_t, _vp, _vp, _vp, _i32, ctypes.c_float, _vp]),
+    "tx_linear_single_push": (_i32, [_u64, _vp, _vp, _vp, _i32, _i32, _vp, _vp]),
+    "tx_aux_peer_reduce_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, ctypes.c_float, _vp, _i32, _vp, _vp]),
+    "tx_aux_peer_best_token": (_i32, [_vp, _vp, ctypes.c_longlong, _vp, _i32, _i32, _vp, _vp, _vp]),
+    "tx_prefetch": (_i32, [_u64, ctypes.c_size_t, ctypes.c_size_t, _vp]),
+    "tx_prefetch_with_next_launch": (_i32, [_u64, ctypes.c_size_t, ctypes.c_size_t]),
 }
 
 
@@ -364,6 +372,79 @@ class _Extension:
     def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
         tokens, two_i = gate_up.shape
         self._check(self._lib.tx_aux_silu_mul(gate_up.data_ptr(), out.data_ptr(), tokens, two_i // 2, self._stream(gate_up)))
+
+    def linear_single_info(self, handle: int) -> tuple[bool, int, int]:
+        """(eligible for the single-token kernel, suggested K splits, bytes of a staged token)."""
+        out = (ctypes.c_int64 * 3)()
+        self._check(self._lib.tx_linear_single_info(handle, out))
+        return bool(out[0]), int(out[1]), int(out[2])
+
+    def linear_single(self, handle: int, x: torch.Tensor | None, y: torch.Tensor | None, *, staged: torch.Tensor | None = None,
+                      swiglu: bool = False, partials: torch.Tensor | None = None) -> None:
+        """One token through the single-token decode kernel: input ``x`` (bf16 ``[1, K]``) or ``staged``
+        (uint8 buffer written by ``add_rmsnorm_single``); output ``y`` (bf16) or ``partials`` (fp32
+        ``[splits, stride]``)."""
+        source = next((t for t in (x, staged, y, partials) if t is not None), None)
+        if source is None:
+            raise RuntimeError("pass the token either as bf16 or in staged form")
+        splits, stride = (partials.shape[0], partials.stride(0)) if partials is not None else (1, 0)
+        self._check(self._lib.tx_linear_single(handle, x.data_ptr() if x is not None else None,
+                                               staged.data_ptr() if staged is not None else None, int(swiglu),
+                                               y.data_ptr() if y is not None else None,
+                                               partials.data_ptr() if partials is not None else None, splits, stride,
+                                               self._stream(source)))
+
+    def add_rmsnorm_single(self, h: torch.Tensor, weight: torch.Tensor, eps: float, *, delta: torch.Tensor | None = None,
+                           partials: torch.Tensor | None = None, y: torch.Tensor | None = None,
+                           staged: torch.Tensor | None = None) -> None:
+        """``h += delta`` (bf16 ``delta`` or fp32 ``partials [splits, stride]``); ``y`` / ``staged`` = rmsnorm(h) * weight."""
+        splits, stride = (partials.shape[0], partials.stride(0)) if partials is not None else (0, 0)
+        self._check(self._lib.tx_aux_add_rmsnorm_single(h.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                                        partials.data_ptr() if partials is not None else None, splits, stride,
+                                                        weight.data_ptr(), y.data_ptr() if y is not None else None,
+                                                        staged.data_ptr() if staged is not None else None, h.numel(), float(eps),
+                                                        self._stream(h)))
+
+    def linear_single_push(self, handle: int, x: torch.Tensor | None, peers, *, staged: torch.Tensor | None = None) -> None:
+        """Row-parallel linear of one token whose bf16 partial row goes straight into every rank's packet
+        inbox (``peers``: a ``tp.PeerExchange``)."""
+        source = x if x is not None else staged
+        self._check(self._lib.tx_linear_single_push(handle, x.data_ptr() if x is not None else None,
+                                                    staged.data_ptr() if staged is not None else None, peers.packet_ptrs,
+                                                    peers.rank, peers.world, peers.packet_epoch.data_ptr(), self._stream(source)))
+
+    def peer_reduce_rmsnorm(self, h: torch.Tensor, weight: torch.Tensor, eps: float, *, peers=None, delta: torch.Tensor | None = None,
+                            y: torch.Tensor | None = None, staged: torch.Tensor | None = None) -> None:
+        """``h += sum over ranks of the packets in this rank's inbox`` (``peers`` given) or ``h += delta``;
+        ``y`` / ``staged`` = rmsnorm(h) * weight.  One thread-block cluster."""
+        self._check(self._lib.tx_aux_peer_reduce_rmsnorm(
+            h.data_ptr(), delta.data_ptr() if delta is not None else None, weight.data_ptr(),
+            y.data_ptr() if y is not None else None, staged.data_ptr() if staged is not None else None, h.numel(), float(eps),
+            peers.packet_inbox.data_ptr() if peers is not None else None, peers.world if peers is not None else 0,
+            peers.packet_epoch.data_ptr() if peers is not None else None, self._stream(h)))
+
+    def peer_best_token(self, score: torch.Tensor, token: torch.Tensor, offset: int, peers, next_token: torch.Tensor) -> None:
+        """Vocabulary-parallel arg-max: this rank's (score fp32, token int64 + offset) against all ranks'."""
+        self._check(self._lib.tx_aux_peer_best_token(score.data_ptr(), token.data_ptr(), int(offset), peers.token_ptrs, peers.rank,
+                                                     peers.world, peers.token_epoch.data_ptr(), next_token.data_ptr(),
+                                                     self._stream(score)))
+
+    def payload_bytes(self, handle: int) -> int:
+        """Size of the packed device payload of a handle (rows padded to 16, columns to 128)."""
+        m, k = self._shapes[handle][:2]
+        return ((m + 15) // 16) * ((k + 127) // 128) * 1024
+
+    def prefetch(self, handle: int, offset: int = 0, nbytes: int | None = None, device_tensor: torch.Tensor | None = None) -> None:
+        """Pull part of a handle's payload into L2 with a small kernel on the current stream."""
+        nbytes = self.payload_bytes(handle) - offset if nbytes is None else nbytes
+        device = self._shapes[handle][2]
+        self._check(self._lib.tx_prefetch(handle, offset, nbytes, torch.cuda.current_stream(device).cuda_stream))
+
+    def prefetch_with_next_launch(self, handle: int, offset: int = 0, nbytes: int | None = None) -> None:
+        """Let the next kernel launched through this library also pull ``[offset, offset + nbytes)`` of the
+        handle's payload into L2 (a hint: results never depend on it)."""
+        nbytes = self.payload_bytes(handle) - offset if nbytes is None else nbytes
+        self._check(self._lib.tx_prefetch_with_next_launch(handle, offset, nbytes))
 
     def kernel_status(self, clear: bool = False, device: int | None = None) -> int:
         """0 when no kernel of this library ever gave up on a bounded wait on this device."""

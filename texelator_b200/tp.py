@@ -107,12 +107,17 @@ def install_tp(model: nn.Module, weights: Path, rank: int, world: int, group=Non
 
 
 class PeerExchange:
-    """Peer-mapped buffers for ``tx_aux_allreduce_add_rmsnorm``: every rank owns an inbox of
-    ``2 * world * hidden`` bf16 values and ``2 * world`` flag words in symmetric memory
-    (``torch.distributed._symmetric_memory``: plain peer mappings over NVLink, no multicast object is
-    bound), plus a local epoch word.  ``inbox_ptrs`` / ``flag_ptrs`` are ctypes arrays with the address of
-    every rank's buffer as seen from this rank.  Construction is collective over ``group`` and raises when
-    symmetric memory cannot be set up, in which case callers keep the NCCL all-reduce.
+    """Peer-mapped buffers of the fused tensor-parallel exchanges, in symmetric memory
+    (``torch.distributed._symmetric_memory``: plain peer mappings over NVLink, no multicast object is bound):
+
+    * ``packet_inbox``: ``2 * world * hidden / 4`` 16-byte packets for ``tx_linear_single_push`` /
+      ``tx_aux_peer_reduce_rmsnorm`` with the epoch word ``packet_epoch``;
+    * ``token_inbox``: ``2 * world`` packets for ``tx_aux_peer_best_token`` with ``token_epoch``;
+    * ``inbox`` / ``flags`` / ``epoch``: the first-generation layout of ``tx_aux_allreduce_add_rmsnorm``.
+
+    ``*_ptrs`` are ctypes arrays with the address of every rank's buffer as seen from this rank.
+    Construction is collective over ``group`` and raises when symmetric memory cannot be set up, in which
+    case callers keep the NCCL all-reduce.
     """
 
     def __init__(self, hidden: int, device: torch.device, group=None):
@@ -127,14 +132,24 @@ class PeerExchange:
         with torch.cuda.device(device):
             self.inbox = symm_mem.empty(2 * self.world * hidden, dtype=torch.bfloat16, device=device)
             self.flags = symm_mem.empty(2 * self.world, dtype=torch.int32, device=device)
+            self.packet_inbox = symm_mem.empty(2 * self.world * (hidden // 4) * 4, dtype=torch.int32, device=device)
+            self.token_inbox = symm_mem.empty(2 * self.world * 4, dtype=torch.int32, device=device)
             self.inbox.zero_()
             self.flags.zero_()
+            self.packet_inbox.zero_()
+            self.token_inbox.zero_()
             inbox_handle = symm_mem.rendezvous(self.inbox, group)
             flag_handle = symm_mem.rendezvous(self.flags, group)
+            packet_handle = symm_mem.rendezvous(self.packet_inbox, group)
+            token_handle = symm_mem.rendezvous(self.token_inbox, group)
             self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+            self.packet_epoch = torch.zeros(1, dtype=torch.int32, device=device)
+            self.token_epoch = torch.zeros(1, dtype=torch.int32, device=device)
             torch.cuda.synchronize(device)
         dist.barrier(group)            # every rank's zeroes are in place before anyone publishes a flag
         pointers = ctypes.c_void_p * self.world
         self.inbox_ptrs = pointers(*[int(p) for p in inbox_handle.buffer_ptrs])
         self.flag_ptrs = pointers(*[int(p) for p in flag_handle.buffer_ptrs])
-        self._handles = (inbox_handle, flag_handle)     # keep the mappings alive
+        self.packet_ptrs = pointers(*[int(p) for p in packet_handle.buffer_ptrs])
+        self.token_ptrs = pointers(*[int(p) for p in token_handle.buffer_ptrs])
+        self._handles = (inbox_handle, flag_handle, packet_handle, token_handle)     # keep the mappings alive
