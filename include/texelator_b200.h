@@ -100,19 +100,6 @@ int tx_linear_static_scratch(uint64_t handle, const void *x, void *y, int tokens
 int tx_linear_fused(uint64_t handle, const void *x, const void *delta, const void *norm_weight, float eps, void *residual_out,
                     int swiglu, void *y, int tokens, int dtype, void *stream);
 
-/* No counterpart in the reference.  B200's L2 (126 MB) holds most of a decoder layer's BC4 payload, and
- * between two weight streams the memory system idles (norms, attention, kernel boundaries).  These two
- * calls ask it to pull bytes [offset, offset + nbytes) of a handle's packed payload (M*K/2 bytes, rows
- * padded to 16 and columns to 128) into L2 ahead of the linear that will stream them; `offset` must be
- * a multiple of 8192, the range is clipped to the payload.  Purely a hint: results never depend on it.
- *   tx_prefetch                   launches a tiny kernel of its own on `stream`;
- *   tx_prefetch_with_next_launch  attaches the request to the next kernel this thread launches through
- *                                 tx_linear, tx_linear_fused, tx_aux_add_rmsnorm,
- *                                 tx_aux_allreduce_add_rmsnorm or tx_aux_attention_step (its thread
- *                                 blocks issue the prefetches as they start); nbytes = 0 cancels. */
-int tx_prefetch(uint64_t handle, size_t offset, size_t nbytes, void *stream);
-int tx_prefetch_with_next_launch(uint64_t handle, size_t offset, size_t nbytes);
-
 /* No counterpart in the reference.  One token through the single-token decode kernel with the two
  * extras a decode loop uses (the handle must be on TX_DECODE_ALU_MMA with the software palette and no
  * low-mode block; tx_linear_single_info tells):
@@ -123,6 +110,9 @@ int tx_prefetch_with_next_launch(uint64_t handle, size_t offset, size_t nbytes);
  *                    ranges, scale (and, in split 0, bias) applied, not rounded.  Their sum in split order
  *                    is the linear's output; tx_aux_add_rmsnorm_single consumes them.  K-split work items
  *                    spread matrices with few rows over all SMs.  `splits` must divide ceil(K/128).
+ * The kernel hands the tensor cores the masked index fields themselves and applies the endpoints to
+ * per-block sums, so it executes fewer instructions per weight than the general kernel, but staging a bf16
+ * token costs it more: it pays off when the token arrives staged.
  * tx_linear_single_info: out[0] = 1 if the handle qualifies, out[1] = number of splits this library
  * would choose for it on this device, out[2] = bytes of the staged form of one token of this K. */
 int tx_linear_single(uint64_t handle, const void *x, const void *staged, int swiglu, void *y, float *y_partial, int splits,

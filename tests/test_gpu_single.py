@@ -1,5 +1,5 @@
 """Single-token decode path on the GPU: the kernel without per-weight arithmetic, K-split partial
-outputs, staged activations from the norm kernel and L2 prefetch hints (run with ``-m gpu``)."""
+outputs and staged activations from the norm kernel (run with ``-m gpu``)."""
 import numpy as np
 import pytest
 import torch
@@ -104,29 +104,6 @@ def test_staged_activations_from_the_norm_kernel(ext, lut, hidden, m):
         assert torch.equal(got, want)
     finally:
         ext.free(handle)
-
-
-def test_prefetch_hints_change_nothing(ext, lut):
-    handle, blocks, scales, x, _ = _case(ext, lut, 2048, 2048, 99)
-    other, *_ = _case(ext, lut, 4096, 1024, 98)
-    try:
-        want = ext.linear(handle, x)
-        ext.prefetch(other)
-        ext.prefetch_with_next_launch(other, 8192, 100000)
-        assert torch.equal(ext.linear(handle, x), want)
-        ext.prefetch_with_next_launch(other)
-        h = torch.randn(1, 2048, device="cuda").bfloat16()
-        y = torch.empty_like(h)
-        ext.add_rmsnorm(h, None, torch.ones(2048, device="cuda", dtype=torch.bfloat16), y, 1e-6)
-        torch.cuda.synchronize()
-        with pytest.raises(RuntimeError, match="multiple of 8192"):
-            ext.prefetch_with_next_launch(other, 100, 8192)
-        with pytest.raises(RuntimeError, match="behind the payload"):
-            ext.prefetch(other, ext.payload_bytes(other), 8192)
-        assert ext.kernel_status() == 0
-    finally:
-        ext.free(handle)
-        ext.free(other)
 
 
 def test_single_token_path_refuses_other_payloads(ext, lut):

@@ -15,7 +15,6 @@
 namespace tx {
 
 static thread_local std::string g_error;
-static thread_local PrefetchHint g_prefetch_hint;
 static std::atomic<long long> g_launches{0};
 static std::mutex g_workspace_guard;
 static std::map<int, Workspace> g_workspaces;
@@ -26,27 +25,6 @@ int fail(int code, const std::string &message) {
   return code;
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
-PrefetchHint take_prefetch_hint() {
-  PrefetchHint hint = g_prefetch_hint;
-  g_prefetch_hint = PrefetchHint{};
-  return hint;
-}
-
-__global__ void prefetch_kernel(const PrefetchHint hint) {
-  grid_launch_dependents();
-  prefetch_l2_chunks(hint, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
-}
-
-// [offset, offset + nbytes) of the payload as whole chunks (the readable pad behind the payload absorbs the round-up)
-static int make_prefetch_hint(const Handle *h, size_t offset, size_t nbytes, PrefetchHint &hint) {
-  const size_t payload = size_t(h->MT) * h->KI * kUnitBytes;
-  if (offset % kPrefetchChunk) return fail(TX_EINVAL, "prefetch offset must be a multiple of 8192 bytes");
-  if (offset >= payload) return fail(TX_EINVAL, "prefetch offset lies behind the payload");
-  nbytes = std::min(nbytes, payload - offset);
-  hint.base = h->tiles + offset;
-  hint.chunks = unsigned((nbytes + kPrefetchChunk - 1) / kPrefetchChunk);
-  return TX_OK;
-}
 bool pdl_enabled() {
   static const bool enabled = [] {
     const char *value = std::getenv("TEXELATOR_B200_NO_PDL");
@@ -286,34 +264,6 @@ int tx_linear_fused(uint64_t handle, const void *x, const void *delta, const voi
                              swiglu != 0, static_cast<__nv_bfloat16 *>(y), tokens, static_cast<cudaStream_t>(stream_ptr));
   if (current != h->device) cudaSetDevice(current);
   return rc;
-}
-
-int tx_prefetch_with_next_launch(uint64_t handle, size_t offset, size_t nbytes) {
-  Handle *h = as_handle(handle);
-  if (!h) return fail(TX_EINVAL, "null Texelator handle");
-  if (nbytes == 0) {
-    g_prefetch_hint = PrefetchHint{};
-    return TX_OK;
-  }
-  return make_prefetch_hint(h, offset, nbytes, g_prefetch_hint);
-}
-
-int tx_prefetch(uint64_t handle, size_t offset, size_t nbytes, void *stream_ptr) {
-  Handle *h = as_handle(handle);
-  if (!h) return fail(TX_EINVAL, "null Texelator handle");
-  if (nbytes == 0) return TX_OK;
-  PrefetchHint hint;
-  int rc = make_prefetch_hint(h, offset, nbytes, hint);
-  if (rc != TX_OK) return rc;
-  int current = 0;
-  TX_CUDA(cudaGetDevice(&current));
-  if (current != h->device) TX_CUDA(cudaSetDevice(h->device));
-  const unsigned blocks = std::min(148u, (hint.chunks + 127u) / 128u);
-  cudaError_t status = launch_pdl(prefetch_kernel, dim3(blocks), dim3(128), 0, static_cast<cudaStream_t>(stream_ptr), hint);
-  count_launch();
-  if (current != h->device) cudaSetDevice(current);
-  TX_CUDA(status);
-  return TX_OK;
 }
 
 int tx_set_lookahead(uint64_t handle, int lookahead) {

@@ -28,10 +28,9 @@ constexpr int kNormChunks = 4;            // hidden <= 512 * 8 * 4 = 16384 stays
 
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16 *__restrict__ h, const __nv_bfloat16 *__restrict__ delta,
                                                                    const __nv_bfloat16 *__restrict__ weight, __nv_bfloat16 *__restrict__ y,
-                                                                   int hidden, float eps, const PrefetchHint hint) {
+                                                                   int hidden, float eps) {
   __shared__ float partial[kNormThreads / 32];
   grid_launch_dependents();
-  prefetch_l2_chunks(hint, blockIdx.x * kNormThreads + threadIdx.x, gridDim.x * kNormThreads);
   grid_dependency_wait();
   const int row = blockIdx.x, chunks = hidden / 8;
   uint4 *hr = reinterpret_cast<uint4 *>(h + size_t(row) * hidden);
@@ -105,11 +104,10 @@ struct NormExtras {
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_single_kernel(__nv_bfloat16 *__restrict__ h, const __nv_bfloat16 *__restrict__ delta,
                                                                           const __nv_bfloat16 *__restrict__ weight,
                                                                           __nv_bfloat16 *__restrict__ y, int hidden, float eps,
-                                                                          const NormExtras extra, const PrefetchHint hint) {
+                                                                          const NormExtras extra) {
   __shared__ float partial[kNormThreads / 32];
   __shared__ unsigned peak[kNormThreads / 32];
   grid_launch_dependents();
-  prefetch_l2_chunks(hint, threadIdx.x, kNormThreads);
   grid_dependency_wait();
   const int chunks = hidden / 8, lane = threadIdx.x & 31;
   uint4 *hr = reinterpret_cast<uint4 *>(h);
@@ -224,11 +222,9 @@ __global__ void __launch_bounds__(kNormThreads) allreduce_add_rmsnorm_kernel(__n
                                                                              const __nv_bfloat16 *__restrict__ weight,
                                                                              __nv_bfloat16 *__restrict__ y, int hidden, float eps,
                                                                              PeerTable peers, int rank, int world,
-                                                                             unsigned *__restrict__ epoch_word, int *__restrict__ status,
-                                                                             const PrefetchHint hint) {
+                                                                             unsigned *__restrict__ epoch_word, int *__restrict__ status) {
   __shared__ float partial_ss[kNormThreads / 32];
   grid_launch_dependents();
-  prefetch_l2_chunks(hint, threadIdx.x, kNormThreads);
   grid_dependency_wait();
   const int chunks = hidden / 8;
   const unsigned epoch = __ldcg(epoch_word) + 1;
@@ -343,7 +339,7 @@ struct ReduceParams {
   float eps;
 };
 
-__global__ void __launch_bounds__(kReduceThreads) peer_reduce_rmsnorm_kernel(const ReduceParams p, const PrefetchHint hint) {
+__global__ void __launch_bounds__(kReduceThreads) peer_reduce_rmsnorm_kernel(const ReduceParams p) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   __shared__ float ss_all[kReduceCluster];
@@ -353,7 +349,6 @@ __global__ void __launch_bounds__(kReduceThreads) peer_reduce_rmsnorm_kernel(con
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int ctas = int(cluster.num_blocks()), cta = int(cluster.block_rank());
   grid_launch_dependents();
-  prefetch_l2_chunks(hint, cta * kReduceThreads + tid, ctas * kReduceThreads);
   grid_dependency_wait();
   const int chunks = p.hidden / 8;
   const int per = (((chunks + ctas - 1) / ctas) + 1) & ~1;            // even: the two chunks of a block stay in one warp
@@ -726,7 +721,7 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_kernel(const _
                                                                       __nv_bfloat16 *__restrict__ k_cache,
                                                                       __nv_bfloat16 *__restrict__ v_cache, float *__restrict__ partial,
                                                                       __nv_bfloat16 *__restrict__ out, int q_heads, int kv_heads,
-                                                                      int max_len, int split_capacity, float scale, const PrefetchHint hint) {
+                                                                      int max_len, int split_capacity, float scale) {
   __shared__ __align__(16) float q_s[GROUP][kHeadDim];
   __shared__ float p_s[GROUP][kStepKeys];
   __shared__ __align__(16) float red_s[kStepThreads / 32][GROUP][kHeadDim];   // per-warp partial sums
@@ -737,7 +732,6 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_kernel(const _
   const int split = blockIdx.x, kvh = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   grid_launch_dependents();
-  prefetch_l2_chunks(hint, (blockIdx.y * gridDim.x + blockIdx.x) + gridDim.x * gridDim.y * tid, gridDim.x * gridDim.y * kStepThreads);
   grid_dependency_wait();
   const long long pos = __ldcg(position);                       // attends to keys 0..pos; key pos is new
   const int live = int(pos / kStepKeys) + 1;                    // splits that hold at least one key
@@ -946,7 +940,7 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_loop_kernel(co
                                                                       __nv_bfloat16 *__restrict__ k_cache,
                                                                       __nv_bfloat16 *__restrict__ v_cache, float *__restrict__ partial,
                                                                       __nv_bfloat16 *__restrict__ out, int q_heads, int kv_heads,
-                                                                      int max_len, int split_capacity, float scale, const PrefetchHint hint) {
+                                                                      int max_len, int split_capacity, float scale) {
   __shared__ __align__(16) float q_s[GROUP][kHeadDim];
   __shared__ float p_s[GROUP][kStepKeys];
   __shared__ __align__(16) float red_s[kStepThreads / 32][GROUP][kHeadDim];   // per-warp partial sums
@@ -963,7 +957,6 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_loop_kernel(co
   const int chunks = int(pos / kStepKeys) + 1;                  // 64-key chunks that hold at least one key
   const int splits = gridDim.x;                                 // CTA `split` takes chunks split, split + splits, ...
   const int live = min(splits, chunks);                         // CTAs with work
-  prefetch_l2_chunks(hint, (blockIdx.y * gridDim.x + blockIdx.x) + gridDim.x * gridDim.y * tid, gridDim.x * gridDim.y * kStepThreads);
   if (split >= live) return;
   const size_t q_rows = size_t(q_heads) * kHeadDim, kv_rows = size_t(kv_heads) * kHeadDim;
 
@@ -1210,12 +1203,11 @@ template <int GROUP, bool LOOP>
 static cudaError_t launch_attention_step(int splits, int kv_heads, cudaStream_t s, const __nv_bfloat16 *qkv, const float *cos_table,
                                          const float *sin_table, const long long *position, __nv_bfloat16 *k_cache,
                                          __nv_bfloat16 *v_cache, float *scratch, __nv_bfloat16 *out, int q_heads, int max_len, float scale) {
-  const PrefetchHint hint = take_prefetch_hint();
   if (LOOP)
     return launch_pdl(attention_step_loop_kernel<GROUP>, dim3(splits, kv_heads), dim3(kStepThreads), 0, s, qkv, cos_table, sin_table, position,
-                      k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale, hint);
+                      k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale);
   return launch_pdl(attention_step_kernel<GROUP>, dim3(splits, kv_heads), dim3(kStepThreads), 0, s, qkv, cos_table, sin_table, position,
-                    k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale, hint);
+                    k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale);
 }
 
 }  // namespace tx
@@ -1229,7 +1221,7 @@ int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, 
     return fail(TX_EINVAL, "tx_aux_add_rmsnorm: hidden must be a multiple of 8 and at most 16384");
   TX_CUDA(launch_pdl(add_rmsnorm_kernel, dim3(tokens), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
                      static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(delta),
-                     static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps, take_prefetch_hint()));
+                     static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;
@@ -1250,7 +1242,7 @@ int tx_aux_add_rmsnorm_single(void *h, const void *delta, const float *partials,
   extra.KI = (hidden + 127) / 128;
   TX_CUDA(launch_pdl(add_rmsnorm_single_kernel, dim3(1), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
                      static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(delta),
-                     static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps, extra, take_prefetch_hint()));
+                     static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps, extra));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;
@@ -1277,7 +1269,7 @@ int tx_aux_allreduce_add_rmsnorm(void *h, const void *partial, const void *weigh
   TX_CUDA(launch_pdl(allreduce_add_rmsnorm_kernel, dim3(1), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
                      static_cast<__nv_bfloat16 *>(h), static_cast<const __nv_bfloat16 *>(partial),
                      static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(y), hidden, eps, table, rank, world,
-                     static_cast<unsigned *>(epoch_word), ws ? ws->status : nullptr, take_prefetch_hint()));
+                     static_cast<unsigned *>(epoch_word), ws ? ws->status : nullptr));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;
@@ -1340,7 +1332,7 @@ int tx_aux_peer_reduce_rmsnorm(void *h, const void *delta, const void *weight, v
   attributes[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attributes;
   config.numAttrs = pdl_enabled() ? 2 : 1;
-  TX_CUDA(cudaLaunchKernelEx(&config, peer_reduce_rmsnorm_kernel, p, take_prefetch_hint()));
+  TX_CUDA(cudaLaunchKernelEx(&config, peer_reduce_rmsnorm_kernel, p));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;

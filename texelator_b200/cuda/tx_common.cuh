@@ -195,15 +195,6 @@ __device__ __forceinline__ uint4 load_packet(const uint4 *src) {
   return v;
 }
 
-// A pending request "bring these bytes of a payload into L2": set by tx_prefetch_with_next_launch on
-// the calling thread, taken (and cleared) by the next kernel launch of this library on that thread.
-struct PrefetchHint {
-  const uint8_t *base = nullptr;
-  unsigned chunks = 0;           // kPrefetchChunk-byte pieces
-};
-constexpr unsigned kPrefetchChunk = 8192;
-PrefetchHint take_prefetch_hint();
-
 void set_error(const std::string &message);
 int fail(int code, const std::string &message);
 Workspace *workspace_for(int device);  // allocates on first use (never inside a launch path)
@@ -304,20 +295,6 @@ __device__ __forceinline__ float palette_value_of(int palette, int e0, int e1, i
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-// L2 prefetch of payload bytes that a later kernel will stream (the 126 MB L2 holds most of a layer).
-// Fire and forget: cp.async.bulk.prefetch.L2 has no completion to wait for.  Thread `first` of `stride`
-// takes chunks first, first + stride, ...
-__device__ __forceinline__ void prefetch_l2_chunks(const PrefetchHint hint, unsigned first, unsigned stride) {
-  for (unsigned c = first; c < hint.chunks; c += stride) {
-#ifdef TX_PREFETCH_LINES
-    for (unsigned line = 0; line < kPrefetchChunk / 128; ++line)
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(hint.base + size_t(c) * kPrefetchChunk + line * 128) : "memory");
-#else
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(hint.base + size_t(c) * kPrefetchChunk), "r"(kPrefetchChunk) : "memory");
-#endif
-  }
-}
 
 bool pdl_enabled();
 

@@ -10,17 +10,10 @@ __device__ __forceinline__ uint4 lds128(unsigned addr) {
   asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
-// Weight loads: read once, so they bypass L1 and are marked evict-first in L2 -- lines that were
-// prefetched for a later kernel (prefetch_l2_chunks) then outlive the stream passing through.
-__device__ __forceinline__ unsigned long long stream_policy() {
-  unsigned long long policy;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-  return policy;
-}
-__device__ __forceinline__ uint4 ldg_stream(const uint4 *p, unsigned long long policy) {
+__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.b32 {%0,%1,%2,%3}, [%4], %5;"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
+  asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
 __device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,

@@ -56,8 +56,11 @@ struct GemvParams {
   const __nv_bfloat16 *gamma;   // [K]
   __nv_bfloat16 *residual_out;  // [T, K] or null: receives bf16(x + delta); must not alias x
   float eps;
-  PrefetchHint prefetch;        // payload bytes of a later linear to pull into L2 while this one runs
-  // single-token kernel only
+};
+
+// extras of the single-token kernel (kept out of GemvParams: the general kernel measured 4 % slower with
+// the larger parameter block)
+struct SoloExtras {
   const uint8_t *staged;        // the token in staged form (tx_decode.cuh) or null: stage p.x in the kernel
   float *y_partial;             // [splits][partial_stride] fp32 row sums of the K ranges, or null: bf16 to y
   size_t partial_stride;
@@ -135,12 +138,11 @@ gemv_tile_kernel(const GemvParams p) {
   int pcount = 0;
   uint4 pend[LOOKAHEAD][2];
   unsigned pflag[LOOKAHEAD];
-  const unsigned long long policy = stream_policy();
   auto prefetch = [&](int slot) {
     if (unext < unit_limit) {                  // (one shared padding unit would be a hot spot for every warp's tail)
       const uint4 *src = p.tiles + size_t(unext) * 64 + lane;
-      pend[slot][0] = ldg_stream(src, policy);
-      pend[slot][1] = ldg_stream(src + 32, policy);
+      pend[slot][0] = ldg_stream(src);
+      pend[slot][1] = ldg_stream(src + 32);
       if (LOWMODE) pflag[slot] = p.flags[unext];
     }
     const bool wrap = pcount == per_tile - 1;
@@ -149,7 +151,6 @@ gemv_tile_kernel(const GemvParams p) {
   };
 #pragma unroll
   for (int i = 0; i < LOOKAHEAD; ++i) prefetch(i);
-  prefetch_l2_chunks(p.prefetch, blockIdx.x + gridDim.x * tid, gridDim.x * kGemvThreads);
 
   if (tid < 16) zero_g[tid] = make_uint4(0, 0, 0, 0);
   // Everything above touched only the immutable payload and shared memory; the activations below are
@@ -462,13 +463,13 @@ __device__ __forceinline__ void mma_f16_zero(float (&c)[4], unsigned a0, unsigne
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
-// Work items: an item is one 16-row tile, or with p.splits > 1 the s-th of `splits` equal K ranges of
+// Work items: an item is one 16-row tile, or with e.splits > 1 the s-th of `splits` equal K ranges of
 // a tile (item = tile * splits + s).  K-split items make matrices with few row tiles (5120 rows = 320
 // tiles on 296 resident CTAs) fill the machine evenly; their fp32 row sums go to p.y_partial[s][row]
 // and whoever consumes the linear adds the `splits` vectors in split order (the residual add + RMSNorm
 // kernel does).  Units of item `it` are it * KIs .. it * KIs + KIs - 1 of the payload (KIs = KI / splits).
 template <int LOOKAHEAD, bool SWIGLU>
-__global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kernel(const GemvParams p, const SoloExtras e) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const unsigned sbase = unsigned(__cvta_generic_to_shared(smem_raw));
   float *tokmul = reinterpret_cast<float *>(smem_raw);
@@ -482,7 +483,7 @@ __global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kern
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int g = lane >> 2, t = lane & 3;
-  const int KI = p.KI, S = p.splits, KIs = KI / S, items = p.MT * S;
+  const int KI = p.KI, S = e.splits, KIs = KI / S, items = p.MT * S;
   const int WS = KIs < kGemvWarps ? KIs : kGemvWarps;
   const bool worker = warp < WS;
   const int per_item = worker ? (KIs - warp + WS - 1) / WS : 0;
@@ -493,12 +494,11 @@ __global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kern
   const unsigned step_unit = WS, step_item = unsigned(item_stride) * unsigned(KIs) - unsigned(per_item - 1) * unsigned(WS);
   int pcount = 0;
   uint4 pend[LOOKAHEAD][2];
-  const unsigned long long policy = stream_policy();
   auto prefetch = [&](int slot) {
     if (unext < unit_limit) {
       const uint4 *src = p.tiles + size_t(unext) * 64 + lane;
-      pend[slot][0] = ldg_stream(src, policy);
-      pend[slot][1] = ldg_stream(src + 32, policy);
+      pend[slot][0] = ldg_stream(src);
+      pend[slot][1] = ldg_stream(src + 32);
     }
     const bool wrap = pcount == per_item - 1;
     unext += wrap ? step_item : step_unit;
@@ -506,7 +506,6 @@ __global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kern
   };
 #pragma unroll
   for (int i = 0; i < LOOKAHEAD; ++i) prefetch(i);
-  prefetch_l2_chunks(p.prefetch, blockIdx.x + gridDim.x * tid, gridDim.x * kGemvThreads);
   grid_launch_dependents();
   grid_dependency_wait();
 
@@ -514,13 +513,13 @@ __global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kern
   {
     const int chunks = p.K / 8, padded = p.KP / 8;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
-    if (p.staged) {
+    if (e.staged) {
       // the kernel that produced the activations wrote them in staged form (tx_decode.cuh): copy
-      const uint4 *src = reinterpret_cast<const uint4 *>(p.staged + kStagedHeader);
+      const uint4 *src = reinterpret_cast<const uint4 *>(e.staged + kStagedHeader);
       uint4 *dst = reinterpret_cast<uint4 *>(stab_g);
       const int total = KI * 18;
       for (int i = tid; i < total; i += kGemvThreads) dst[i] = __ldcg(src + i);
-      if (tid == 0) tokmul[0] = __ldcg(reinterpret_cast<const float *>(p.staged));
+      if (tid == 0) tokmul[0] = __ldcg(reinterpret_cast<const float *>(e.staged));
     } else {
       const uint4 *xp = reinterpret_cast<const uint4 *>(p.x);
       uint4 held[kXChunks];
@@ -577,7 +576,7 @@ __global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kern
     }
   };
 
-  const unsigned epoch = p.push.world ? __ldcg(p.push.epoch_word) + 1u : 0u;   // after the dependency wait: the previous
+  const unsigned epoch = e.push.world ? __ldcg(e.push.epoch_word) + 1u : 0u;   // after the dependency wait: the previous
                                                                                // exchange's consumer advanced the word
   float acc0 = 0.f, acc1 = 0.f;                    // rows g and g+8: sum over this lane's blocks of delta * G
   float base[4] = {0.f, 0.f, 0.f, 0.f};            // base term, column 0 (lanes t == 0: base[0] row g, base[2] row g+8)
@@ -646,7 +645,7 @@ __global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kern
         acc0 = acc1 = 0.f;
         base[0] = base[1] = base[2] = base[3] = 0.f;
         asm volatile("bar.sync 1, %0;" ::"r"(workers) : "memory");
-        if (p.push.world) {
+        if (e.push.world) {
           // tensor-parallel partial: packets of four consecutive rows into every rank's inbox (warp 0)
           if (tid < 32) {
             unsigned bits = 0;
@@ -660,9 +659,9 @@ __global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kern
             const unsigned b3 = __shfl_down_sync(0xffffffffu, bits, 3);
             const int row = (item / S) * 16 + tid;
             if (tid < 16 && (tid & 3) == 0 && row < p.M) {
-              const size_t at = (size_t(epoch & 1u) * p.push.world + p.push.rank) * p.push.packets + (row >> 2);
-              for (int peer = 0; peer < p.push.world; ++peer)
-                store_packet(p.push.inbox[peer] + at, bits | (b1 << 16), b2 | (b3 << 16), epoch);
+              const size_t at = (size_t(epoch & 1u) * e.push.world + e.push.rank) * e.push.packets + (row >> 2);
+              for (int peer = 0; peer < e.push.world; ++peer)
+                store_packet(e.push.inbox[peer] + at, bits | (b1 << 16), b2 | (b3 << 16), epoch);
             }
           }
         } else if (row_live) {
@@ -677,8 +676,8 @@ __global__ void __launch_bounds__(kGemvThreads, TX_SOLO_MIN_CTAS) gemv_solo_kern
             const float gate = __bfloat162float(__float2bfloat16(fmaf(sum, row_scale * tm, row_bias)));
             const float up = __bfloat162float(__float2bfloat16(fmaf(up_sum, up_scale * tm, up_bias)));
             p.y[tile * 8 + tid] = __float2bfloat16(gate / (1.f + __expf(-gate)) * up);
-          } else if (p.y_partial) {
-            p.y_partial[size_t(item % S) * p.partial_stride + tile * 16 + tid] = fmaf(sum, row_scale * tm, row_bias);
+          } else if (e.y_partial) {
+            e.y_partial[size_t(item % S) * e.partial_stride + tile * 16 + tid] = fmaf(sum, row_scale * tm, row_bias);
           } else {
             p.y[tile * 16 + tid] = __float2bfloat16(fmaf(sum, row_scale * tm, row_bias));
           }
@@ -841,8 +840,10 @@ static GemvKernel pick_kernel(int lookahead, int nt, bool pre, bool low_mode, in
 // texture-unit palette's uneven interpolation weights need the variant that carries the extra code.
 static bool needs_generic_variant(const Handle *h) { return h->has_low_mode || h->palette == TX_PALETTE_HARDWARE; }
 
+using SoloKernel = void (*)(const GemvParams, const SoloExtras);
+
 template <bool SWIGLU>
-static GemvKernel pick_solo(int lookahead) {
+static SoloKernel pick_solo(int lookahead) {
   switch (lookahead) {
     case 1: return gemv_solo_kernel<1, SWIGLU>;
     case 2: return gemv_solo_kernel<2, SWIGLU>;
@@ -873,6 +874,7 @@ static int tokens_per_pass(int KP) {
 
 struct GemvPlan {
   GemvKernel kernel;
+  SoloKernel solo_kernel;
   int nt, grid;
   bool pre, solo;
   size_t smem;
@@ -891,7 +893,8 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, 
   plan.solo = single_token_kernel;
   if (plan.solo) {
     plan.pre = false;
-    plan.kernel = (fuse & kFuseSwiglu) ? pick_solo<true>(h->lookahead) : pick_solo<false>(h->lookahead);
+    plan.kernel = nullptr;
+    plan.solo_kernel = (fuse & kFuseSwiglu) ? pick_solo<true>(h->lookahead) : pick_solo<false>(h->lookahead);
     plan.smem = solo_smem_bytes(h->KI);
   } else {
     plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre, needs_generic_variant(h), fuse);
@@ -903,11 +906,12 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, 
   int per_sm = 0;
   {
     std::lock_guard<std::mutex> lock(guard);
-    auto key = std::make_tuple(h->device, reinterpret_cast<const void *>(plan.kernel), plan.smem);
+    const void *entry = plan.solo ? reinterpret_cast<const void *>(plan.solo_kernel) : reinterpret_cast<const void *>(plan.kernel);
+    auto key = std::make_tuple(h->device, entry, plan.smem);
     auto hit = cache.find(key);
     if (hit == cache.end()) {
-      TX_CUDA(cudaFuncSetAttribute(plan.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
-      TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, plan.kernel, kGemvThreads, plan.smem));
+      TX_CUDA(cudaFuncSetAttribute(entry, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
+      TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, entry, kGemvThreads, plan.smem));
       cache[key] = per_sm;
     } else {
       per_sm = hit->second;
@@ -944,8 +948,6 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
     p.T = n;
     p.KP = KP;
     p.palette = h->palette;
-    p.splits = 1;
-    p.prefetch = take_prefetch_hint();
     if (plan.pre) {
       // scaled fp16 activations go through the per-device scratch (one pre-pass CTA per token)
       if (size_t(n) * KP > ws->xprep_halfs) return fail(TX_EINVAL, "tokens*K exceeds the activation scratch of the decode GEMV");
@@ -992,8 +994,6 @@ int launch_gemv_fused(const Handle *h, const __nv_bfloat16 *x, const __nv_bfloat
   p.gamma = gamma;
   p.residual_out = residual_out;
   p.eps = eps;
-  p.splits = 1;
-  p.prefetch = take_prefetch_hint();
   TX_CUDA(launch_pdl(plan.kernel, dim3(plan.grid), dim3(kGemvThreads), plan.smem, stream, p));
   count_launch();
   TX_CUDA(cudaGetLastError());
@@ -1050,14 +1050,14 @@ int launch_gemv_single(const Handle *h, const __nv_bfloat16 *x, const uint8_t *s
   p.T = 1;
   p.KP = h->KI * 128;
   p.palette = h->palette;
-  p.staged = staged;
-  p.y_partial = y_partial;
-  p.partial_stride = partial_stride;
-  p.splits = splits;
-  if (push) p.push = *push;
-  p.prefetch = take_prefetch_hint();
+  SoloExtras e{};
+  e.staged = staged;
+  e.y_partial = y_partial;
+  e.partial_stride = partial_stride;
+  e.splits = splits;
+  if (push) e.push = *push;
   const int grid = std::max(1, std::min(h->MT * splits, ws->sm_count * 2));
-  TX_CUDA(launch_pdl(plan.kernel, dim3(grid), dim3(kGemvThreads), plan.smem, stream, p));
+  TX_CUDA(launch_pdl(plan.solo_kernel, dim3(grid), dim3(kGemvThreads), plan.smem, stream, p, e));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;

@@ -241,13 +241,12 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
       src[m] = p.tiles + (size_t(live[m] ? rt : 0) * p.KI) * 64 + half0 * 32 + lane;
       fl[m] = p.flags + size_t(live[m] ? rt : 0) * p.KI;
     }
-    const unsigned long long policy = stream_policy();
     uint4 q[MT][kHalvesPerWarp];
     unsigned flag[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
 #pragma unroll
-      for (int h = 0; h < kHalvesPerWarp; ++h) q[m][h] = ldg_stream(src[m] + h * 32, policy);
+      for (int h = 0; h < kHalvesPerWarp; ++h) q[m][h] = ldg_stream(src[m] + h * 32);
       flag[m] = fl[m][0];
     }
     bool ok = true;
@@ -261,7 +260,7 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
         for (int h = 0; h < kHalvesPerWarp; ++h) cq[m][h] = q[m][h];
         if (unit + 1 < p.KI) {                           // next unit in flight while this one is decoded
 #pragma unroll
-          for (int h = 0; h < kHalvesPerWarp; ++h) q[m][h] = ldg_stream(src[m] + size_t(unit + 1) * 64 + h * 32, policy);
+          for (int h = 0; h < kHalvesPerWarp; ++h) q[m][h] = ldg_stream(src[m] + size_t(unit + 1) * 64 + h * 32);
           flag[m] = fl[m][unit + 1];
         }
       }

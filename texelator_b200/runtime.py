@@ -76,8 +76,6 @@ C_API = {
     "tx_linear_single_push": (_i32, [_u64, _vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "tx_aux_peer_reduce_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, ctypes.c_float, _vp, _i32, _vp, _vp]),
     "tx_aux_peer_best_token": (_i32, [_vp, _vp, ctypes.c_longlong, _vp, _i32, _i32, _vp, _vp, _vp]),
-    "tx_prefetch": (_i32, [_u64, ctypes.c_size_t, ctypes.c_size_t, _vp]),
-    "tx_prefetch_with_next_launch": (_i32, [_u64, ctypes.c_size_t, ctypes.c_size_t]),
 }
 
 
@@ -175,7 +173,8 @@ class _Extension:
         _Extension._bias_keepalive = contiguous
         return contiguous.data_ptr(), (DTYPE_BF16 if contiguous.dtype == torch.bfloat16 else DTYPE_F16)
 
-    def linear(self, handle: int, x: torch.Tensor) -> torch.Tensor:
+    def _activation(self, handle: int, x: torch.Tensor) -> tuple[int, int, int, int]:
+        """The checks of texelator_cuda.cu:1332-1337 on an activation tensor; returns (M, K, device, tokens)."""
         shape = self._shapes.get(handle)
         if shape is None:
             raise RuntimeError("null Texelator handle")
@@ -184,23 +183,27 @@ class _Extension:
             raise RuntimeError("input must be contiguous CUDA FP16 or BF16")
         if x.size(-1) != k or x.get_device() != device:
             raise RuntimeError("input shape/device mismatch")
-        tokens = x.numel() // k
+        return m, k, device, x.numel() // k
+
+    @staticmethod
+    def _dtype_flag(x: torch.Tensor) -> int:
+        return DTYPE_BF16 if x.dtype == torch.bfloat16 else DTYPE_F16
+
+    def linear(self, handle: int, x: torch.Tensor) -> torch.Tensor:
+        m, k, device, tokens = self._activation(handle, x)
         y = torch.empty(x.shape[:-1] + (m,), dtype=x.dtype, device=x.device)
-        if tokens == 0:
-            return y
-        stream = torch.cuda.current_stream(device).cuda_stream
-        dtype = DTYPE_BF16 if x.dtype == torch.bfloat16 else DTYPE_F16
-        self._check(self._lib.tx_linear(handle, x.data_ptr(), y.data_ptr(), tokens, dtype, stream))
+        if tokens:
+            self._check(self._lib.tx_linear(handle, x.data_ptr(), y.data_ptr(), tokens, self._dtype_flag(x),
+                                            torch.cuda.current_stream(device).cuda_stream))
         return y
 
     def linear_out(self, handle: int, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
         """``linear`` into a caller-provided output (static buffers for CUDA graphs)."""
-        m, k, device = self._shapes[handle]
-        tokens = x.numel() // k
-        if y.numel() != tokens * m or y.dtype != x.dtype or not y.is_contiguous() or not x.is_contiguous():
+        m, k, device, tokens = self._activation(handle, x)
+        if y.numel() != tokens * m or y.dtype != x.dtype or not y.is_contiguous() or y.device != x.device:
             raise RuntimeError("input shape/device mismatch")
-        stream = torch.cuda.current_stream(device).cuda_stream
-        self._check(self._lib.tx_linear(handle, x.data_ptr(), y.data_ptr(), tokens, DTYPE_BF16, stream))
+        self._check(self._lib.tx_linear(handle, x.data_ptr(), y.data_ptr(), tokens, self._dtype_flag(x),
+                                        torch.cuda.current_stream(device).cuda_stream))
         return y
 
     def linear_static_scratch(self, handle: int, x: torch.Tensor) -> torch.Tensor:
@@ -223,11 +226,11 @@ class _Extension:
         residual stream (``x + delta`` is rounded to bf16, stored to ``residual_out`` and RMS-normalised
         first); with ``swiglu`` the handle's rows are (gate, up) pairs (``interleave_gate_up`` order) and
         ``y`` is ``[tokens, M/2]``.  At most two tokens."""
-        m, k, device = self._shapes[handle]
-        tokens = x.numel() // k
+        m, k, device, tokens = self._activation(handle, x)
         for tensor in (x, y, norm_weight, delta, residual_out):
-            if tensor is not None and (not tensor.is_cuda or tensor.dtype != torch.bfloat16 or not tensor.is_contiguous()):
-                raise RuntimeError("fused linear tensors must be contiguous CUDA BF16")
+            if tensor is not None and (not tensor.is_cuda or tensor.dtype != torch.bfloat16 or not tensor.is_contiguous()
+                                       or tensor.get_device() != device):
+                raise RuntimeError("fused linear tensors must be contiguous CUDA BF16 on the handle's device")
         if y.numel() != tokens * (m // 2 if swiglu else m):
             raise RuntimeError("output has the wrong size for this handle")
         ptr = lambda t: t.data_ptr() if t is not None else None
@@ -429,23 +432,6 @@ class _Extension:
                                                      peers.world, peers.token_epoch.data_ptr(), next_token.data_ptr(),
                                                      self._stream(score)))
 
-    def payload_bytes(self, handle: int) -> int:
-        """Size of the packed device payload of a handle (rows padded to 16, columns to 128)."""
-        m, k = self._shapes[handle][:2]
-        return ((m + 15) // 16) * ((k + 127) // 128) * 1024
-
-    def prefetch(self, handle: int, offset: int = 0, nbytes: int | None = None, device_tensor: torch.Tensor | None = None) -> None:
-        """Pull part of a handle's payload into L2 with a small kernel on the current stream."""
-        nbytes = self.payload_bytes(handle) - offset if nbytes is None else nbytes
-        device = self._shapes[handle][2]
-        self._check(self._lib.tx_prefetch(handle, offset, nbytes, torch.cuda.current_stream(device).cuda_stream))
-
-    def prefetch_with_next_launch(self, handle: int, offset: int = 0, nbytes: int | None = None) -> None:
-        """Let the next kernel launched through this library also pull ``[offset, offset + nbytes)`` of the
-        handle's payload into L2 (a hint: results never depend on it)."""
-        nbytes = self.payload_bytes(handle) - offset if nbytes is None else nbytes
-        self._check(self._lib.tx_prefetch_with_next_launch(handle, offset, nbytes))
-
     def kernel_status(self, clear: bool = False, device: int | None = None) -> int:
         """0 when no kernel of this library ever gave up on a bounded wait on this device."""
         value = self._lib.tx_kernel_status(self._device_index(device), int(clear))
@@ -476,13 +462,11 @@ def extension(verbose: bool = False):
     return _EXTENSION
 
 
-def _linear_dispatch(handle: int, x: torch.Tensor) -> torch.Tensor:
-    # texelator/runtime.py:120-130 (the opt-in FP4 experiment is not part of this build)
-    return extension().linear(handle, x)
-
-
 class TexelatorLinear(nn.Module):
-    """texelator/runtime.py:133-145."""
+    """Drop-in for an ``nn.Linear`` whose weight lives in one or more BC4 handles (the reference's module of
+    the same name, texelator/runtime.py:133-145; it splits outputs taller than a texture allows into
+    several handles, and lists of handles keep that shape here).  Each handle yields a slice of the output
+    features; ``bias`` is only used when the handles themselves carry none."""
 
     def __init__(self, handles: list[int], bias: nn.Parameter | None = None):
         super().__init__()
@@ -492,14 +476,18 @@ class TexelatorLinear(nn.Module):
         self.bias = bias
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        contiguous = x.contiguous()
-        outputs = [_linear_dispatch(handle, contiguous) for handle in self.handles]
-        output = outputs[0] if len(outputs) == 1 else torch.cat(outputs, dim=-1)
-        return output if self.bias is None else output + self.bias
+        ext = extension()
+        x = x.contiguous()
+        if len(self.handles) == 1:
+            y = ext.linear(self.handles[0], x)
+        else:
+            y = torch.cat([ext.linear(handle, x) for handle in self.handles], dim=-1)
+        return y if self.bias is None else y + self.bias
 
 
 class DecodeOnlyLinear(nn.Module):
-    """texelator/runtime.py:148-157."""
+    """Single-token calls go to the BC4 module, everything else to the dense original
+    (texelator/runtime.py:148-157: the opt-in "fp16 prefill" mode)."""
 
     def __init__(self, original: nn.Module, quantized: nn.Module):
         super().__init__()
@@ -507,26 +495,8 @@ class DecodeOnlyLinear(nn.Module):
         self.quantized = quantized
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if x.numel() == x.shape[-1]:
-            return self.quantized(x)
-        return self.original(x)
-
-
-def _cpu_u8(path: Path) -> torch.Tensor:
-    return torch.from_numpy(np.fromfile(path, dtype=np.uint8).copy())
-
-
-def _cpu_f32(path: Path) -> torch.Tensor:
-    return torch.from_numpy(np.fromfile(path, dtype="<f4").copy())
-
-
-def pack_entry(weights: Path, entry: dict, bias: torch.Tensor | None = None, lookahead: int = 1) -> int:
-    """texelator/runtime.py:168-176."""
-    ext = extension()
-    handle = ext.pack_encoded(_cpu_u8(weights / entry["blocks_file"]), _cpu_f32(weights / entry["scales_file"]), bias)
-    ext.set_lookahead(handle, lookahead)
-    ext.set_prefill(handle, PREFILL_THRESHOLD, PREFILL_TILE_ROWS)
-    return handle
+        one_token = x.numel() == x.shape[-1]
+        return (self.quantized if one_token else self.original)(x)
 
 
 def palette_of(weights: Path) -> int:
@@ -541,81 +511,107 @@ def palette_of(weights: Path) -> int:
     return PALETTE_HARDWARE if recorded == REFERENCE_TEXTURE_PALETTE_SHA256 else PALETTE_SOFTWARE
 
 
+class _EncodedMatrix:
+    """The two files of one ``metadata.json`` entry (``<key>.bc4`` row-major blocks, ``<key>.scales.f32``),
+    memory-mapped, handed out as row slabs."""
+
+    def __init__(self, weights: Path, entry: dict):
+        self.m, self.k = int(entry["M"]), int(entry["K"])
+        self.blocks = np.memmap(Path(weights) / entry["blocks_file"], dtype=np.uint8, mode="r", shape=(self.m, self.k // 2))
+        self.scales = np.memmap(Path(weights) / entry["scales_file"], dtype="<f4", mode="r", shape=(self.m,))
+
+    def slabs(self, rows: int):
+        for first in range(0, self.m, rows):
+            last = min(first + rows, self.m)
+            yield (first, last, torch.from_numpy(np.array(self.blocks[first:last]).reshape(-1)),
+                   torch.from_numpy(np.array(self.scales[first:last])))
+
+
 def pack_entry_handles(weights: Path, entry: dict, bias: torch.Tensor | None = None, lookahead: int = 1,
                        max_texture_rows: int = 32768, palette: int | None = None) -> list[int]:
-    """Pack one matrix, splitting very tall outputs into independent handles
-    (texelator/runtime.py:179-207; the reference needs the split for the texture height limit,
-    it is kept so handle lists look the same)."""
-    m, k = int(entry["M"]), int(entry["K"])
+    """Handles for one encoded matrix, one per slab of ``max_texture_rows`` output rows (the reference
+    splits at the texture height limit, texelator/runtime.py:179-207; the split is kept so that handle
+    lists look the same).  Every handle gets the look-ahead, the default prefill settings and the palette
+    the artefact was encoded against."""
     if max_texture_rows <= 0:
         raise ValueError("max_texture_rows must be positive")
-    row_bytes = (k // 16) * 8
-    raw_blocks = np.memmap(weights / entry["blocks_file"], dtype=np.uint8, mode="r", shape=(m, row_bytes))
-    raw_scales = np.memmap(weights / entry["scales_file"], dtype="<f4", mode="r", shape=(m,))
     ext = extension()
     palette = palette_of(weights) if palette is None else palette
     handles: list[int] = []
     try:
-        for start in range(0, m, max_texture_rows):
-            stop = min(start + max_texture_rows, m)
-            block_tensor = torch.from_numpy(np.ascontiguousarray(raw_blocks[start:stop]).reshape(-1))
-            scale_tensor = torch.from_numpy(np.ascontiguousarray(raw_scales[start:stop]))
-            handle = ext.pack_encoded(block_tensor, scale_tensor, bias[start:stop] if bias is not None else None)
+        for first, last, blocks, scales in _EncodedMatrix(weights, entry).slabs(max_texture_rows):
+            handle = ext.pack_encoded(blocks, scales, None if bias is None else bias[first:last])
+            handles.append(handle)
             ext.set_lookahead(handle, lookahead)
             ext.set_prefill(handle, PREFILL_THRESHOLD, PREFILL_TILE_ROWS)
             ext.set_palette(handle, palette)
-            handles.append(handle)
     except Exception:
         free(handles)
         raise
+    return handles
+
+
+def pack_entry(weights: Path, entry: dict, bias: torch.Tensor | None = None, lookahead: int = 1) -> int:
+    """One handle for the whole matrix (texelator/runtime.py:168-176)."""
+    return pack_entry_handles(weights, entry, bias, lookahead, max_texture_rows=int(entry["M"]))[0]
+
+
+def _swap_linears(model: nn.Module, weights: Path, entries: list[dict], lookahead: int, locate, wrap) -> list[int]:
+    """Pack every entry and put ``wrap(original, handles)`` in the place ``locate(entry)`` names; on any
+    failure the handles made so far are released."""
+    handles: list[int] = []
+    try:
+        for entry in entries:
+            parent, child = resolve_parent(model, locate(entry))
+            original = getattr(parent, child)
+            made = wrap(original, entry)
+            setattr(parent, child, made[0])
+            handles.extend(made[1])
+    except Exception:
+        free(handles)
+        raise
+    model._texelator_handles = handles
     return handles
 
 
 def install(model: nn.Module, weights: Path, lookahead: int = 1, fp16_prefill: bool = False) -> list[int]:
-    """Replace the linears named in ``weights/metadata.json`` (texelator/runtime.py:210-239)."""
-    metadata = json.loads((weights / "metadata.json").read_text())
-    handles: list[int] = []
-    for entry in metadata["entries"]:
-        parent, child = resolve_parent(model, entry["module_name"])
-        original = getattr(parent, child)
+    """Replace the linears listed in ``weights/metadata.json`` of a CUDA-resident model
+    (texelator/runtime.py:210-239).  The handles take over the original bias."""
+    weights = Path(weights)
+
+    def wrap(original, entry):
         device = original.weight.device
         if device.type != "cuda":
             raise RuntimeError(f"{entry['module_name']} is on {device}; selected linears must be CUDA resident")
-        bias = original.bias if getattr(original, "bias", None) is not None else None
         with torch.cuda.device(device):
-            entry_handles = pack_entry_handles(weights, entry, bias=bias, lookahead=lookahead)
-        quantized = TexelatorLinear(entry_handles)
-        setattr(parent, child, DecodeOnlyLinear(original, quantized) if fp16_prefill else quantized)
-        handles.extend(entry_handles)
-        if not fp16_prefill:
-            del original
+            made = pack_entry_handles(weights, entry, bias=getattr(original, "bias", None), lookahead=lookahead)
+        module = TexelatorLinear(made)
+        return (DecodeOnlyLinear(original, module) if fp16_prefill else module), made
+
+    handles = _swap_linears(model, weights, json.loads((weights / "metadata.json").read_text())["entries"], lookahead,
+                            lambda entry: entry["module_name"], wrap)
     gc.collect()
     if torch.cuda.is_available():
         torch.cuda.empty_cache()
-    model._texelator_handles = handles
     return handles
 
 
 def install_standalone(model: nn.Module, weights: Path, entries: list[dict], name_mapper, lookahead: int = 1) -> list[int]:
-    """Replace meta-initialised linears without dense source weights (texelator/runtime.py:242-263)."""
-    handles: list[int] = []
-    try:
-        for entry in entries:
-            parent, child = resolve_parent(model, name_mapper(entry["module_name"]))
-            original = getattr(parent, child)
-            entry_handles = pack_entry_handles(weights, entry, lookahead=lookahead)
-            setattr(parent, child, TexelatorLinear(entry_handles, bias=getattr(original, "bias", None)))
-            handles.extend(entry_handles)
-    except Exception:
-        free(handles)
-        raise
-    model._texelator_handles = handles
-    return handles
+    """Replace meta-initialised linears that never had dense weights (texelator/runtime.py:242-263); the
+    bias stays a module parameter because it is loaded after the handles are made."""
+    weights = Path(weights)
+
+    def wrap(original, entry):
+        made = pack_entry_handles(weights, entry, lookahead=lookahead)
+        return TexelatorLinear(made, bias=getattr(original, "bias", None)), made
+
+    return _swap_linears(model, weights, entries, lookahead, lambda entry: name_mapper(entry["module_name"]), wrap)
 
 
 def free(handles: list[int]) -> None:
-    """texelator/runtime.py:266-274."""
+    """Release handles after the device has finished with them (texelator/runtime.py:266-274)."""
     if torch.cuda.is_available():
         torch.cuda.synchronize()
+    ext = extension()
     for handle in handles:
-        extension().free(handle)
+        ext.free(handle)
