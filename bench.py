@@ -27,6 +27,12 @@ import torch
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+# DRAM bytes moved per algorithmic byte by the decode GEMV: dram__bytes_read.sum + dram__bytes_write.sum of
+# one ncu-captured gemv_tile_kernel<4,1,0,0,0> launch on a 34816x5120 matrix (89.34 MB + 3.27 MB) over its
+# algorithmic 89.35 MB.  The kernel reads every payload byte once, so the ratio carries over to the other
+# shapes; re-capture when the kernel's memory access pattern changes.
+GEMV_DRAM_BYTES_PER_ALGORITHMIC_BYTE = (89.34 + 3.27) / 89.35
+
 METRIC = "bc4_decode_tokens_per_second_bs1"
 UNIT = "tok/s"
 
@@ -90,7 +96,8 @@ class ClockSampler:
 # then a dense matmul), written with multi-threaded torch ops, on one projection-sized sample.
 # ---------------------------------------------------------------------------------------------
 
-def cpu_dequant_matmul(blocks: np.ndarray, scales: np.ndarray, x: torch.Tensor, lut: torch.Tensor) -> torch.Tensor:
+def cpu_dequant(blocks: np.ndarray, scales: np.ndarray, lut: torch.Tensor) -> torch.Tensor:
+    """Palette-LUT gather times the fp32 row scale, rounded to bf16: the matrix the operator multiplies by."""
     m = scales.shape[0]
     raw = torch.from_numpy(blocks).reshape(m, -1, 8)
     e0 = raw[:, :, 0].view(torch.int8).long() + 127
@@ -101,15 +108,20 @@ def cpu_dequant_matmul(blocks: np.ndarray, scales: np.ndarray, x: torch.Tensor, 
     sel = (word[:, :, None] >> (3 * torch.arange(16))[None, None, :]) & 7
     pal = lut[e1, e0]                                               # [m, nb, 8]
     w = torch.gather(pal, 2, sel).reshape(m, -1) * torch.from_numpy(scales)[:, None]
-    return (x.float() @ w.bfloat16().float().T).bfloat16()
+    return w.bfloat16().float()
+
+
+def cpu_matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return (x.float() @ w.T).bfloat16()
 
 
 _CPU_CACHE: dict = {}
 
 
 def cpu_baseline_sample(config, seconds: float = 10.0) -> dict:
-    """Time dequantise-then-matmul on a row slab of one hidden x hidden projection sized to take
-    about ``seconds`` on this host, and extrapolate linearly (bytes) to one decoded token."""
+    """Time dequantise-then-matmul on a row slab of one hidden x hidden projection sized to take about
+    ``seconds`` on this host, and scale by bytes to one decoded token.  Reports the combined figure
+    (``value``) and the matmul on already dequantised weights alone (``matmul_only``)."""
     from oracle import bc4_oracle as O
     k = config.hidden
     torch.set_num_threads(max(torch.get_num_threads(), os.cpu_count() or 1))   # torchrun pins OMP_NUM_THREADS=1
@@ -120,9 +132,9 @@ def cpu_baseline_sample(config, seconds: float = 10.0) -> dict:
         blocks, scales = O.encode_minmax(w, lut_np)
         x = torch.randn(1, k).bfloat16()
         lut = torch.from_numpy(lut_np)
-        cpu_dequant_matmul(blocks, scales, x, lut)                   # warm
+        cpu_matmul(x, cpu_dequant(blocks, scales, lut))              # warm
         start = time.perf_counter()
-        cpu_dequant_matmul(blocks, scales, x, lut)
+        cpu_matmul(x, cpu_dequant(blocks, scales, lut))
         per_row = (time.perf_counter() - start) / 256
         _CPU_CACHE.update(lut=lut, blocks=blocks, scales=scales, x=x, per_row=per_row)
     c = _CPU_CACHE
@@ -130,14 +142,19 @@ def cpu_baseline_sample(config, seconds: float = 10.0) -> dict:
     blocks = np.tile(c["blocks"].reshape(256, -1), (rows // 256, 1)).reshape(-1)
     scales = np.tile(c["scales"], rows // 256)
     start = time.perf_counter()
-    cpu_dequant_matmul(blocks, scales, c["x"], c["lut"])
-    elapsed = time.perf_counter() - start
+    weights = cpu_dequant(blocks, scales, c["lut"])
+    middle = time.perf_counter()
+    for _ in range(3):
+        cpu_matmul(c["x"], weights)
+    end = time.perf_counter()
+    dequant_s, matmul_s = middle - start, (end - middle) / 3
     sample_bytes = rows * k // 2 + 4 * rows
-    return {"value": (sample_bytes / config.bc4_bytes_per_token()) / elapsed, "unit": UNIT,
+    fraction = sample_bytes / config.bc4_bytes_per_token()
+    return {"value": fraction / (dequant_s + matmul_s), "unit": UNIT, "matmul_only": fraction / matmul_s,
             "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"palette-LUT dequant + fp32 matmul of a {rows}x{k} BC4 slab ({sample_bytes} B of the "
-                      f"{config.bc4_bytes_per_token()} B read per token), extrapolated linearly to one token",
-            "seconds": elapsed}
+            "sample": f"palette-LUT dequant ({dequant_s:.3f} s) + fp32 matmul ({matmul_s * 1e3:.1f} ms) of a {rows}x{k} BC4 slab "
+                      f"({sample_bytes} B of the {config.bc4_bytes_per_token()} B read per token), scaled by bytes to one token",
+            "sample_fraction_of_token": fraction, "seconds": dequant_s + matmul_s}
 
 
 def workload_config(config, prompt: int, world: int, lookahead: int) -> dict:
@@ -151,24 +168,24 @@ def workload_config(config, prompt: int, world: int, lookahead: int) -> dict:
 
 
 def run_reference_arm(args, config) -> None:
+    """The reference's CPU arithmetic on this host.  One step = one bounded sample of the workload (a slab of
+    one projection); ``ms_per_step`` is the measured time of that sample, ``value`` the tokens per second it
+    corresponds to when scaled by bytes to a whole token (``cpu_baseline.sample_fraction_of_token``)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    values = []
     per_step = max(0.5, min(5.0, 150.0 / max(args.steps + args.warmup, 1)))   # whole run within minutes
     for _ in range(args.warmup):
         cpu_baseline_sample(config, per_step)
-    for _ in range(args.steps):
-        values.append(cpu_baseline_sample(config, per_step))
-    best = max(values, key=lambda v: v["value"])
-    value = float(np.median([v["value"] for v in values]))
-    best = dict(best, value=value)
+    samples = [cpu_baseline_sample(config, per_step) for _ in range(args.steps)]
+    value = float(np.median([v["value"] for v in samples]))
+    middle = min(samples, key=lambda v: abs(v["value"] - value))
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": dict(workload_config(config, args.prompt, args.gpus, args.lookahead),
-                           note="reference arm: CPU dequantise-then-matmul on a bounded slab of this workload, extrapolated by bytes"),
-            "cpu_baseline": best,
+            "warmup": args.warmup, "ms_per_step": 1000.0 * float(np.median([v["seconds"] for v in samples])),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(config, args.prompt, args.gpus, args.lookahead),
+            "note": "CPU dequantise-then-matmul on a bounded slab of this workload per step; value is scaled by bytes to one token",
+            "cpu_baseline": dict(middle, value=value),
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -259,14 +276,201 @@ def gemv_roofline(model, config, world: int) -> dict:
     ms = begin.elapsed_time(end) / reps
     peak, source = measured_peaks()
     achieved = total / ms / 1e6
-    # DRAM bytes per algorithmic byte of this kernel, from the ncu capture of one 34816x5120 launch
-    # (dram__bytes_read.sum + dram__bytes_write.sum = 92.25 MB for 89.35 MB; profiles/gemv_tile_kernel_34816x5120.md),
-    # scaled to the launches of one token by the bytes they process
-    traffic_ratio = 92.25 / 89.35
+    traffic_ratio = GEMV_DRAM_BYTES_PER_ALGORITHMIC_BYTE
     return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-            "traffic": traffic_ratio * total, "traffic_source": "ncu, one 34816x5120 launch, scaled by algorithmic bytes",
+            "traffic": traffic_ratio * total, "traffic_source": "ncu capture of one 34816x5120 launch (ratio to algorithmic bytes), scaled by algorithmic bytes",
             "peak_source": source, "kernel": "gemv_tile_kernel (all %d decode GEMV launches of one token)" % len(jobs),
             "algorithmic_bytes_per_token": total, "ms_per_token_linear_only": ms, "launches": len(jobs)}
+
+
+def _pack_random(ext, m: int, k: int, count: int, lut, lookahead: int) -> list[int]:
+    from texelator_b200.modeling import encode_minmax_cuda
+    handles = []
+    for index in range(count):
+        weight = torch.randn(m, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1000 * m + index)) * 0.02
+        handles.append(ext.pack_encoded_device(*encode_minmax_cuda(weight, lut)))
+        ext.set_lookahead(handles[-1], lookahead)
+    return handles
+
+
+def _time_calls(stream, call, repeats: int) -> float:
+    """Milliseconds per call of ``call()`` (CUDA events on ``stream``, after three untimed calls)."""
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            call()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record(stream)
+        for _ in range(repeats):
+            call()
+        end.record(stream)
+        stream.synchronize()
+    return begin.elapsed_time(end) / repeats
+
+
+def prefill_sweep(ext, stream, lookahead: int) -> list[dict]:
+    """BASELINE configuration 3: T in {32, 128, 512} x {5120->5120, 5120->17408, 17408->5120}.  Every point runs
+    every tile candidate over a rotating set of matrices larger than L2 and keeps the fastest (the autotuner's
+    rule; all candidates are bitwise identical)."""
+    from texelator_b200.autotune import CANDIDATES
+    from texelator_b200.modeling import software_palette_table
+    lut = software_palette_table("cuda")
+    peak = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text()).get("bf16_tflops", 1590.0)) if (ROOT / "MEASURED_PEAKS.json").exists() else 1590.0
+    rows = []
+    for k, m in ((5120, 5120), (5120, 17408), (17408, 5120)):
+        copies = max(2, int(160e6 // (m * k // 2)) + 1)
+        handles = _pack_random(ext, m, k, copies, lut, lookahead)
+        try:
+            for tokens in (32, 128, 512):
+                x = torch.randn(tokens, k, device="cuda").bfloat16()
+                y = torch.empty(tokens, m, device="cuda", dtype=torch.bfloat16)
+                best = None
+                for name, backend in CANDIDATES.items():
+                    for h in handles:
+                        ext.set_prefill_backend(h, backend)
+                        ext.set_prefill(h, 1, 1024)
+
+                    def sweep():
+                        for h in handles:
+                            ext.linear_out(h, x, y)
+                    ms = _time_calls(stream, sweep, 5) / copies
+                    if best is None or ms < best[0]:
+                        best = (ms, name)
+                ms, name = best
+                tflops = 2.0 * tokens * m * k / ms / 1e9
+                weight_gbs = (m * k / 2 + 4 * m + 2 * tokens * (k + m)) / ms / 1e6
+                rows.append({"T": tokens, "M": m, "K": k, "ms": ms, "tflops": tflops, "frac_of_bf16_burst": tflops / peak,
+                             "hbm_gbs": weight_gbs, "tile": name})
+        finally:
+            for h in handles:
+                ext.free(h)
+    return rows
+
+
+def gemv_cfg1(ext, stream, lookahead: int) -> dict:
+    """BASELINE configuration 1 as a throughput point: one token through 4096x4096 matrices, a rotating set
+    larger than L2 inside a CUDA graph."""
+    from texelator_b200.modeling import software_palette_table
+    handles = _pack_random(ext, 4096, 4096, 24, software_palette_table("cuda"), lookahead)
+    try:
+        x = torch.randn(1, 4096, device="cuda").bfloat16()
+        y = torch.empty(1, 4096, device="cuda", dtype=torch.bfloat16)
+        with torch.cuda.stream(stream):
+            for h in handles:
+                ext.linear_out(h, x, y)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for h in handles:
+                    ext.linear_out(h, x, y)
+        ms = _time_calls(stream, graph.replay, 10) / len(handles)
+        peak, _ = measured_peaks()
+        gbs = (4096 * 4096 / 2 + 4 * 4096 + 4 * 4096) / ms / 1e6
+        return {"us_per_call": ms * 1e3, "GBps": gbs, "frac": gbs / peak, "matrices": len(handles)}
+    finally:
+        for h in handles:
+            ext.free(h)
+
+
+def tp_parity(config, device, rank: int, world: int, lookahead: int, layers: int = 4) -> dict:
+    """Tensor-parallel result against one GPU, on a reduced layer count of the same shapes: every rank builds its
+    shard of a `layers`-layer model, rank 0 also the unsharded model from the same seed; all decode eight tokens
+    after a 64-token prompt.  Reports whether the ranks hold identical bits, the cosine of the final hidden state
+    of the first decoded token against the one-GPU model, and how many of the eight tokens agree."""
+    import dataclasses
+
+    import torch.distributed as dist
+
+    from texelator_b200.modeling import BC4Decoder
+    small = dataclasses.replace(config, layers=layers, name=f"{config.name}-{layers}layers")
+    ids = torch.randint(0, small.vocab, (64,), generator=torch.Generator().manual_seed(7))
+
+    def decode(model, steps=8):
+        model.prefill(ids)
+        model.tok.fill_(int(ids[-1]))
+        model.capture()
+        tokens, first_hidden = [], None
+        for step in range(steps):
+            model.decode_graph()
+            model.stream.synchronize()
+            tokens.append(int(model.next_tok))
+            if step == 0:
+                first_hidden = model.last_hidden.float().clone()
+        return tokens, first_hidden
+
+    shard = BC4Decoder(small, device, 96, seed=99, tp_rank=rank, tp_world=world, lookahead=lookahead)
+    fused = shard.enable_peer_exchange()
+    tokens, hidden = decode(shard)
+    status = shard.ext.kernel_status(device=device.index)
+    reference = hidden.clone()
+    dist.broadcast(reference, src=0)
+    identical = torch.tensor([int(torch.equal(reference, hidden))], device=device)
+    dist.all_reduce(identical, op=dist.ReduceOp.MIN)
+    shard.graph = None
+    result = {"layers": layers, "fused_exchange": bool(fused), "ranks_identical": bool(identical.item()), "kernel_status": int(status)}
+    if rank == 0:
+        full = BC4Decoder(small, device, 96, seed=99, lookahead=lookahead)
+        full_tokens, full_hidden = decode(full)
+        cosine = float(torch.nn.functional.cosine_similarity(full_hidden.reshape(1, -1), hidden.reshape(1, -1)))
+        agree = sum(int(a == b) for a, b in zip(tokens, full_tokens))
+        result.update(hidden_cosine=cosine, tokens_equal_tp1=agree == len(tokens), tokens_agreeing=agree, tokens_compared=len(tokens))
+        full.graph = None
+        full.free()
+    dist.barrier()
+    return result
+
+
+def micro_exchange(config, device, rank: int, world: int, exchanges: int = 1000) -> dict:
+    """`exchanges` back-to-back exchanges (a 64-row-tile push-linear standing in for the producer, then the
+    cluster reduce + norm) in one CUDA graph: microseconds per exchange at this rank count."""
+    import torch.distributed as dist
+
+    from texelator_b200 import runtime
+    from texelator_b200.modeling import encode_minmax_cuda, software_palette_table
+    from texelator_b200.tp import PeerExchange
+    ext = runtime.extension()
+    hidden, k = config.hidden, 512
+    peers = PeerExchange(hidden, device)
+    handle = ext.pack_encoded_device(*encode_minmax_cuda(torch.randn(hidden, k, device=device) * 0.02, software_palette_table(device)))
+    x = torch.randn(1, k, device=device).bfloat16()
+    h = torch.zeros(1, hidden, device=device, dtype=torch.bfloat16)
+    gamma = torch.ones(hidden, device=device, dtype=torch.bfloat16)
+    y = torch.empty_like(h)
+    stream = torch.cuda.Stream(device)
+
+    def body(count):
+        for _ in range(count):
+            ext.linear_single_push(handle, x, peers)
+            ext.peer_reduce_rmsnorm(h, gamma, 1e-6, peers=peers, y=y)
+
+    def alone(count):
+        for _ in range(count):
+            ext.linear_single(handle, x, y)
+            ext.peer_reduce_rmsnorm(h, gamma, 1e-6, delta=y, y=y)
+
+    times = {}
+    for name, fn in (("exchange", body), ("local", alone)):
+        with torch.cuda.stream(stream):
+            fn(2)
+            stream.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                fn(exchanges)
+            graph.replay()
+            stream.synchronize()
+            dist.barrier()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(stream)
+            graph.replay()
+            end.record(stream)
+            stream.synchronize()
+        elapsed = torch.tensor([begin.elapsed_time(end)], device=device)
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        times[name] = float(elapsed.item()) * 1e3 / exchanges
+    status = ext.kernel_status(device=device.index)
+    ext.free(handle)
+    return {"n_gpus": world, "us_per_exchange_with_producer": times["exchange"], "us_same_kernels_without_exchange": times["local"],
+            "us_exchange_only": times["exchange"] - times["local"], "hidden": hidden, "kernel_status": int(status)}
 
 
 def run_gpu_arm(args, config) -> None:
@@ -295,38 +499,50 @@ def run_gpu_arm(args, config) -> None:
         ms = timed_steps(model, steps, warmup, world, e2e=False)
     ms_e2e = timed_steps(model, steps, warmup, world, e2e=True)
     roofline = gemv_roofline(model, config, world)
+    extras = {}
+    if world == 1 and not args.skip_extras:
+        extras["prefill"] = prefill_sweep(model.ext, model.stream, args.lookahead)
+        extras["gemv_cfg1"] = gemv_cfg1(model.ext, model.stream, args.lookahead)
     # any bounded device wait that ran out (tcgen05 pipeline, peer exchange) leaves a code here; 0 = none
     status = torch.tensor([model.ext.kernel_status()], device=device)
     if world > 1:
         dist.all_reduce(status, op=dist.ReduceOp.MAX)
     kernel_status = int(status.item())
+    model.graph = None
+    if world > 1 and not args.skip_extras:
+        model.free()
+        extras["tp_parity"] = tp_parity(config, device, rank, world, args.lookahead)
+        extras["micro_exchange"] = micro_exchange(config, device, rank, world)
+        kernel_status = max(kernel_status, extras["tp_parity"]["kernel_status"], extras["micro_exchange"]["kernel_status"])
     if rank == 0:
         cpu = cpu_baseline_sample(config)
         line = {
             "metric": METRIC, "value": 1000.0 / ms, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": dict(workload_config(config, prompt, world, args.lookahead),
-                           allreduce=("none" if world == 1 else
-                                      "fused into the norm kernel over NVLink peer memory" if fused_allreduce else "nccl")),
+            "config": workload_config(config, prompt, world, args.lookahead),
+            "allreduce": ("none" if world == 1 else "packets pushed from the linears' epilogues over NVLink peer memory, cluster reduce + norm"
+                          if fused_allreduce else "nccl"),
             "e2e": {"value": 1000.0 / ms_e2e, "unit": UNIT, "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
             "gpu_launches": int(model.launches_per_step * steps),
             "kernel_status": kernel_status,
             "roofline": roofline,
             "cpu_baseline": cpu,
             "clocks": clocks.summary(),
+            **extras,
         }
         print(json.dumps(line), flush=True)
     sys.stdout.flush()
-    # Tear down in an order that cannot block: graphs that captured NCCL kernels go first, every rank
-    # meets at a barrier, and multi-rank runs leave without destroying the communicator (its destructor
-    # can wait for ever on captured work).
-    model.graph = None
+    # Tear down in an order that cannot block: graphs that captured NCCL kernels are gone, every rank meets at
+    # a barrier, and multi-rank runs leave without destroying the communicator (its destructor can wait for
+    # ever on captured work).  A bounded device wait that ran out anywhere makes the run fail.
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
-        os._exit(0)
+        os._exit(0 if kernel_status == 0 else 4)
     model.free()
+    if kernel_status:
+        raise SystemExit(f"a device-side bounded wait ran out (status {kernel_status}): the measurement is invalid")
 
 
 def run_micro(args) -> None:
@@ -381,6 +597,7 @@ def main() -> None:
     parser.add_argument("--decode", type=int, default=512)
     parser.add_argument("--lookahead", type=int, default=4)
     parser.add_argument("--nccl-allreduce", action="store_true", help="tensor parallel: keep NCCL all-reduces (default: fused peer-memory exchange)")
+    parser.add_argument("--skip-extras", action="store_true", help="only the decode measurement (no prefill sweep / cfg1 / parity / exchange timing)")
     parser.add_argument("--layers", type=int, default=0, help="override the layer count (profiling aid; not a bench result)")
     parser.add_argument("--micro", default=None, help="MxK[xT]: time one linear shape alone (profiling aid)")
     parser.add_argument("--backend", type=int, default=5, help="prefill backend id for --micro with T >= 16")

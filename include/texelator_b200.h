@@ -91,7 +91,8 @@ int tx_linear_static_scratch(uint64_t handle, const void *x, void *y, int tokens
  * linears, texelator/cli.py:189-219).  Decode linear with its neighbours fused into the same launch:
  *   norm_weight != NULL : r = bf16(x + delta) (delta may be NULL), a = bf16(rmsnorm(r, eps) * norm_weight)
  *                         feeds the linear; r is also stored to residual_out when that is non-NULL
- *                         (it must not alias x).  K <= 18432.
+ *                         (it must not overlap x, delta or y: one thread block stores it while the others
+ *                         still read their copy of the row).  K <= 18432.
  *   swiglu != 0         : the handle's rows are (gate, up) pairs -- in every group of 16 rows, rows 0-7
  *                         are gate rows and rows 8-15 the matching up rows -- and
  *                         y[t, 8*g + i] = silu(lin[16*g + i]) * lin[16*g + 8 + i]; y is [tokens, M/2].

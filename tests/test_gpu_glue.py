@@ -178,6 +178,9 @@ def test_fused_linear_argument_checks(ext):
         x, y, gamma = torch.zeros(1, 256, **bf), torch.zeros(1, 64, **bf), torch.ones(256, **bf)
         with pytest.raises(RuntimeError, match="alias"):
             ext.linear_fused_out(handle, x, y, norm_weight=gamma, residual_out=x)
+        delta = torch.zeros(1, 256, **bf)
+        with pytest.raises(RuntimeError, match="overlap delta or y"):
+            ext.linear_fused_out(handle, x, y, norm_weight=gamma, delta=delta, residual_out=delta)
         with pytest.raises(RuntimeError, match="norm weight"):
             ext.linear_fused_out(handle, x, y, delta=x)
         with pytest.raises(RuntimeError, match="at most 2 tokens"):

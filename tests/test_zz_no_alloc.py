@@ -37,14 +37,10 @@ def test_static_scratch_linear_matches_regular_linear(lut):
             ext.linear_static_scratch(handle, torch.zeros(40, k, dtype=torch.bfloat16, device="cuda"))
     finally:
         ext.free(handle)
-    big = ext.pack_encoded(torch.from_numpy(np.tile(blocks[: 16 * k // 2], 1)), torch.from_numpy(scales[:16].copy()))
+    wide = O.encode_minmax((rng.standard_normal((16, 32768)) * 0.02).astype(np.float32), lut)
+    huge = ext.pack_encoded(torch.from_numpy(wide[0]), torch.from_numpy(wide[1]))
     try:
-        wide = O.encode_minmax((rng.standard_normal((16, 32768)) * 0.02).astype(np.float32), lut)
-        huge = ext.pack_encoded(torch.from_numpy(wide[0]), torch.from_numpy(wide[1]))
-        try:
-            with pytest.raises(RuntimeError, match="exceeds the built-in activation scratch"):
-                ext.linear_static_scratch(huge, torch.zeros(9, 32768, dtype=torch.bfloat16, device="cuda"))
-        finally:
-            ext.free(huge)
+        with pytest.raises(RuntimeError, match="exceeds the built-in activation scratch"):
+            ext.linear_static_scratch(huge, torch.zeros(9, 32768, dtype=torch.bfloat16, device="cuda"))
     finally:
-        ext.free(big)
+        ext.free(huge)

@@ -362,7 +362,8 @@ int tx_kernel_status(int device, int clear) {
   int current = 0, value = 0;
   TX_CUDA(cudaGetDevice(&current));
   TX_CUDA(cudaSetDevice(device));
-  cudaError_t status = cudaMemcpy(&value, ws->status, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaError_t status = cudaDeviceSynchronize();      // also orders against non-blocking streams, which a plain copy does not
+  if (status == cudaSuccess) status = cudaMemcpy(&value, ws->status, sizeof(int), cudaMemcpyDeviceToHost);
   if (status == cudaSuccess && clear && value) status = cudaMemset(ws->status, 0, sizeof(int));
   cudaSetDevice(current);
   if (status != cudaSuccess) return fail(TX_ECUDA, std::string("tx_kernel_status: ") + cudaGetErrorString(status));

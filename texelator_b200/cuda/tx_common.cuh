@@ -208,7 +208,7 @@ void count_launch(int n = 1);
   } while (0)
 
 // ---------------------------------------------------------------------------------------------
-// Exact software-palette decode of one selector (the table of oracle/bc4_oracle.py):
+// Exact software-palette decode of one selector (BC4-SNORM interpolation, each value rounded once to fp32):
 // value = RN( ((7-g)*e0 + g*e1) / 889 ) in the high mode (e0 > e1),
 //         RN( ((5-g)*e0 + g*e1) / 635 ) in the low mode, selectors 6/7 -> -1/+1.
 // n*c followed by one fused residual correction is the correctly rounded quotient for every

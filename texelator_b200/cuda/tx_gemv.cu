@@ -970,7 +970,17 @@ int launch_gemv_fused(const Handle *h, const __nv_bfloat16 *x, const __nv_bfloat
   const int fuse = (gamma ? kFuseNorm : 0) | (swiglu ? kFuseSwiglu : 0);
   if (!gamma && (delta || residual_out)) return fail(TX_EINVAL, "delta and residual_out need a norm weight");
   if (gamma && h->K > kXChunks * kGemvThreads * 8) return fail(TX_EINVAL, "fused RMSNorm handles K up to 18432");
-  if (residual_out && residual_out == x) return fail(TX_EINVAL, "residual_out must not alias x");
+  if (residual_out) {
+    // CTA 0 stores the new residual while the other CTAs still read x and delta for their own copy of the row
+    auto overlaps = [&](const void *other, size_t bytes) {
+      const char *a = reinterpret_cast<const char *>(residual_out), *b = static_cast<const char *>(other);
+      const size_t mine = size_t(tokens) * h->K * 2;
+      return other && a < b + bytes && b < a + mine;
+    };
+    if (overlaps(x, size_t(tokens) * h->K * 2)) return fail(TX_EINVAL, "residual_out must not alias x");
+    if (overlaps(delta, size_t(tokens) * h->K * 2) || overlaps(y, size_t(tokens) * h->M * 2))
+      return fail(TX_EINVAL, "residual_out must not overlap delta or y");
+  }
   if (swiglu && h->M % 16) return fail(TX_EINVAL, "SwiGLU pairs need M to be a multiple of 16");
   if (fuse == 0) return launch_gemv(h, x, y, tokens, stream);
   GemvPlan plan;
@@ -1120,9 +1130,22 @@ int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfl
   int rc = static_scratch_for(h->device, &scratch);
   if (rc != TX_OK) return rc;
   GemvKernel kernel = pick_kernel(h->lookahead, nt, true, needs_generic_variant(h));
-  TX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
+  // attribute and occupancy are looked up once per (device, kernel variant, shared bytes): host-side table, no allocation on the device
+  static std::mutex guard;
+  static std::map<std::tuple<int, const void *, size_t>, int> cache;
   int per_sm = 0;
-  TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem));
+  {
+    std::lock_guard<std::mutex> lock(guard);
+    auto key = std::make_tuple(h->device, reinterpret_cast<const void *>(kernel), smem);
+    auto hit = cache.find(key);
+    if (hit == cache.end()) {
+      TX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBudget + 1024)));
+      TX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem));
+      cache[key] = per_sm;
+    } else {
+      per_sm = hit->second;
+    }
+  }
   if (per_sm < 1) return fail(TX_EINVAL, "decode GEMV does not fit in shared memory for this K");
   GemvParams p{};
   p.tiles = reinterpret_cast<const uint4 *>(h->tiles);

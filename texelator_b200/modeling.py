@@ -526,6 +526,27 @@ class BC4Decoder:
     def decode_graph(self) -> None:
         self.graph.replay()
 
+    def check_status(self) -> None:
+        """Raise if any kernel of this rank gave up on a bounded wait (a peer that never delivered, a pipeline
+        barrier that never completed): whatever was decoded since the last check cannot be trusted then.
+        Synchronises the device; call it at host synchronisation points (every few tokens, or when a
+        sequence ends), not per launch."""
+        code = self.ext.kernel_status(clear=True, device=self.device.index)
+        if code:
+            raise RuntimeError(f"a device-side bounded wait ran out (status {code}); the tokens decoded since the last check are invalid")
+
+    def decode_tokens(self, count: int, check_every: int = 16) -> list[int]:
+        """Replay the captured step ``count`` times; the device status word is checked every ``check_every``
+        tokens and at the end."""
+        tokens = []
+        for index in range(count):
+            self.graph.replay()
+            if (index + 1) % check_every == 0 or index + 1 == count:
+                self.stream.synchronize()
+                self.check_status()
+            tokens.append(self.next_tok.clone())
+        return [int(t) for t in torch.cat(tokens).tolist()]
+
     def free(self) -> None:
         runtime.free(self.handles)
         self.handles = []
