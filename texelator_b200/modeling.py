@@ -185,7 +185,11 @@ class BC4Decoder:
                 del wq, wk, wv
                 bias = None
                 if c.qkv_bias:
-                    bias = (torch.randn(wqkv.shape[0], device=self.device, generator=gen) * 0.02).bfloat16()
+                    # drawn for the whole projection and then sliced, so every rank of a tensor-parallel
+                    # model sees the weights of the one-GPU model made from the same seed
+                    whole = (torch.randn(c.q_rows + 2 * c.kv_rows, device=self.device, generator=gen) * 0.02).bfloat16()
+                    bq, bk, bv = whole[:c.q_rows], whole[c.q_rows:c.q_rows + c.kv_rows], whole[c.q_rows + c.kv_rows:]
+                    bias = torch.cat([rows_of(bq, self.q_loc), rows_of(bk, self.kv_loc), rows_of(bv, self.kv_loc)]).contiguous()
                 self.h_qkv.append(self._pack_rows(wqkv, lut, bias))
                 del wqkv
                 self.h_o.append(self._pack_columns(randn(c.hidden, c.q_rows), lut))
@@ -509,6 +513,9 @@ class BC4Decoder:
         step = self._decode_step if not use_fused else (self._decode_step_single if self.single and fused is None and not self.fuse_norm and self.prefer_single() else self._decode_step_fused)
         stream = torch.cuda.Stream(self.device)
         saved = (self.tok.clone(), self.pos.clone(), self.mask.clone())
+        # the capture stream is non-blocking: everything queued so far (the prompt's cache writes, the clones
+        # above) has to be ordered before the first warm-up step on it
+        stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(stream):
             for _ in range(2):
                 step()
@@ -521,6 +528,7 @@ class BC4Decoder:
             self.launches_per_step = self.ext.launch_count() - before
             self.tok.copy_(saved[0]); self.pos.copy_(saved[1]); self.mask.copy_(saved[2])
             stream.synchronize()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
         self.stream = stream
 
     def decode_graph(self) -> None:
