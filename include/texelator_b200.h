@@ -31,8 +31,10 @@ extern "C" {
 #define TX_EUNSUPPORTED (-3) /* feature not available on this device/build */
 #define TX_ESTATE (-4)       /* handle not in a state that allows the call */
 
-/* activation / bias element types (the reference accepts fp16 or bf16; this build computes the
- * bf16 operator only -- fp16 activations return TX_EUNSUPPORTED) */
+/* activation / bias element types (the reference accepts fp16 or bf16: texelator_cuda.cu:1332-1335).  tx_linear
+ * computes both; the entry points with no reference counterpart (fused, single-token, static-scratch) and the
+ * TX_DECODE_ALU_EXACT / TX_DECODE_TEXTURE paths are bf16 only.  A handle's bias must have the activations'
+ * type ("input and bias dtypes must match", texelator_cuda.cu:1449). */
 #define TX_DTYPE_F16 0
 #define TX_DTYPE_BF16 1
 
@@ -74,7 +76,12 @@ int tx_pack_encoded_shard(const uint8_t *blocks, size_t nbytes, const float *sca
 
 /* linear(handle, x) -> y: texelator_cuda.cu:1329-1469 (extension.cpp:30).  `x` is a contiguous
  * device [tokens, K] array, `y` a device [tokens, M] array the caller allocated (the reference
- * allocates with at::empty); both of `dtype`.  Asynchronous on `stream`. */
+ * allocates with at::empty); both of `dtype`.  Asynchronous on `stream`.
+ * TX_DTYPE_BF16: y = bf16(sum_k pal * scale_m * x + bias) (texelator_bc4_bf16_kernel, :141-199, rounds the weight
+ * to bf16 first; this build does not, which is inside the operator's tolerance).  TX_DTYPE_F16: the fp16 twin
+ * (texelator_bc4_kernel, :94-139, un-rounded weight, fp32 accumulation, one fp16 rounding; for tokens >=
+ * prefill_threshold the reference goes through fp16(pal*scale) and cuBLAS, :996-1046): the same kernels, the
+ * fp16 activations are the tensor-core operand as they are. */
 int tx_linear(uint64_t handle, const void *x, void *y, int tokens, int dtype, void *stream);
 
 /* No counterpart in the reference.  Same result as tx_linear for a small token group (1..32 tokens,
@@ -160,6 +167,16 @@ int tx_hardware_palette(int device, float *out_host);
  * paths follow it.  With TX_PALETTE_HARDWARE the texture decode path passes the palette gate on
  * devices whose texture unit reproduces that table. */
 int tx_set_palette(uint64_t handle, int palette);
+
+/* encode: the reference's offline encoder for one matrix, texelator/encoder.py:34-102 (endpoint_opt), :23-31
+ * (nearest), :105-117 (pack_blocks) and :137-145 (row scales) -- there a chain of PyTorch tensor operations,
+ * here two kernels whose output is byte-identical to it.  All pointers are device pointers: `weight` fp32
+ * [M, K] row-major, `hdiag` fp32 [K] (the activation second moments E[x_k^2] that weight the error),
+ * `lut` fp32 [255, 255, 8] = palette[e1 + 127][e0 + 127][selector]; writes M * K / 2 bytes of row-major BC4
+ * blocks (the .bc4 file content) and M fp32 row scales (the .scales.f32 content), which tx_pack_encoded
+ * accepts as they are.  Asynchronous on `stream`. */
+int tx_encode(const float *weight, const float *hdiag, const float *lut, int M, int K, uint8_t *blocks_out, float *scales_out,
+              void *stream);
 
 /* New: exact decode of the packed device copy (TX_DEQUANT_*), for bit-exact checks against the
  * encoder's palette.  `out` is a device [M,K] array. */

@@ -188,6 +188,26 @@ def linear_bf16(x_bf16_as_f32: np.ndarray, blocks: np.ndarray, scales: np.ndarra
     return bf16_round((acc + b).astype(np.float32))
 
 
+def linear_f16(x_f16_as_f32: np.ndarray, blocks: np.ndarray, scales: np.ndarray, lut: np.ndarray,
+               bias: np.ndarray | None = None, prefill: bool = False) -> np.ndarray:
+    """Oracle for the fp16 operator.  Decode (texelator_bc4_kernel, texelator_cuda.cu:77-139):
+    ``y = f16( sum_k f32(pal*scale) * f32(x) + f32(bias) )`` -- the weight is *not* rounded.  With ``prefill``
+    (texelator_prefill, :996-1046): the weight is rounded to fp16 (texelator_decode_tile), cuBLAS accumulates in
+    fp32 and stores fp16, and the bias is added to that with ``__hadd`` (:630-634).  Accumulation here is fp64, as
+    in ``linear_bf16``.  Input and output are fp32 arrays holding fp16-representable values."""
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    w = dequant_palette(blocks, scales.shape[0], lut) * scales[:, None]
+    if prefill:
+        w = w.astype(np.float16)
+    acc = np.asarray(x_f16_as_f32, dtype=np.float64) @ w.astype(np.float64).T
+    if bias is None:
+        return acc.astype(np.float16).astype(np.float32)
+    b = np.asarray(bias, dtype=np.float64)[None, :]
+    if prefill:
+        return (acc.astype(np.float16).astype(np.float64) + b).astype(np.float16).astype(np.float32)
+    return (acc + b).astype(np.float16).astype(np.float32)
+
+
 def row_scales(weight: np.ndarray) -> np.ndarray:
     """``scale_m = max(|W[m,:]|, 1e-12)`` (texelator/encoder.py:140)."""
     return np.maximum(np.abs(np.asarray(weight, dtype=np.float32)).max(axis=1), np.float32(1e-12)).astype(np.float32)

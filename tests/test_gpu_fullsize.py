@@ -104,3 +104,48 @@ def test_full_size_row_shards_reassemble_bit_exactly(ext):
     finally:
         for h in shards + [handle]:
             ext.free(h)
+
+
+# BASELINE configuration 3: T in {32, 128, 512} x {5120->5120, 5120->17408, 17408->5120}
+CFG3_SHAPES = [(5120, 5120), (17408, 5120), (5120, 17408)]          # (M, K)
+
+
+@pytest.mark.parametrize("tokens", [32, 128, 512])
+@pytest.mark.parametrize("m,k", CFG3_SHAPES)
+def test_prefill_sweep_points_match_oracle(ext, lut, m, k, tokens):
+    """Every point of the prefill sweep through the tile the autotuner would pick for it (all candidates are
+    bitwise identical, checked here on the fly), against the dequantise-then-matmul oracle on 96 sampled
+    output rows.  The first 512 rows of the matrix carry weights encoded by the restated reference encoder
+    (activation-weighted endpoint search), the rest the min/max fill."""
+    from texelator_b200.modeling import encode_minmax_cuda, software_palette_table
+    gen = torch.Generator(device="cuda").manual_seed(3 * m + k + tokens)
+    weight = torch.randn(m, k, device="cuda", generator=gen) * 0.02
+    blocks, scales = encode_minmax_cuda(weight, software_palette_table("cuda"))
+    calibration = torch.randn(64, k, generator=torch.Generator().manual_seed(k))
+    real_blocks, real_scales = O.encode_linear(weight[:512].cpu(), (calibration * calibration).mean(0), lut)
+    blocks = blocks.clone()
+    blocks[:real_blocks.size] = torch.from_numpy(real_blocks.reshape(-1)).cuda()
+    scales[:512] = torch.from_numpy(real_scales).cuda()
+    x = torch.randn(tokens, k, device="cuda", generator=gen).bfloat16()
+    handle = ext.pack_encoded_device(blocks, scales)
+    try:
+        ext.set_prefill(handle, 16, 32768)
+        outputs = []
+        for backend in (5, 6, 7, 8, 9):
+            ext.set_prefill_backend(handle, backend)
+            outputs.append(ext.linear(handle, x))
+        torch.cuda.synchronize()
+        assert ext.kernel_status() == 0
+        for other in outputs[1:]:
+            assert torch.equal(outputs[0], other)
+        rows = np.sort(np.concatenate([np.random.default_rng(m + tokens).choice(512, 48, replace=False),
+                                       512 + np.random.default_rng(k + tokens).choice(m - 512, 48, replace=False)]))
+        host_blocks = blocks.cpu().numpy().reshape(m, k // 2)
+        ref = O.linear_bf16(x.float().cpu().numpy(), host_blocks[rows].reshape(-1), scales.cpu().numpy()[rows], lut)
+        got = outputs[0].float().cpu().numpy()[:, rows]
+        err = O.rel_rms(got, ref)
+        assert err <= 1e-2, (m, k, tokens, err)
+        cosine = float((got * ref).sum() / np.sqrt((got * got).sum() * (ref * ref).sum()))
+        assert cosine >= 0.9999
+    finally:
+        ext.free(handle)

@@ -16,7 +16,7 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-SOURCES = ["tx_api.cu", "tx_pack.cu", "tx_gemv.cu", "tx_prefill.cu", "tx_aux.cu"]
+SOURCES = ["tx_api.cu", "tx_pack.cu", "tx_gemv.cu", "tx_prefill.cu", "tx_aux.cu", "tx_encode.cu"]
 LIBRARY = HERE / "libtexelator_b200.so"
 STAMP = HERE / ".build_stamp"
 

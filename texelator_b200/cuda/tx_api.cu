@@ -81,8 +81,7 @@ static void destroy(Handle *h) {
 
 static int pack_common(const uint8_t *blocks, size_t src_pitch_blocks, const float *scales, int rows, int bpr,
                        const void *bias_dev, int bias_dtype, int device, uint64_t *out) {
-  if (bias_dev && bias_dtype != TX_DTYPE_BF16)
-    return fail(TX_EUNSUPPORTED, "only a bf16 bias is supported (the fp16 operator is not part of this build)");
+  if (bias_dev && bias_dtype != TX_DTYPE_BF16 && bias_dtype != TX_DTYPE_F16) return fail(TX_EINVAL, "bias must be CUDA FP16 or BF16 [M]");
   int previous = 0;
   cudaGetDevice(&previous);
   cudaError_t status = cudaSetDevice(device);
@@ -118,6 +117,7 @@ static int pack_common(const uint8_t *blocks, size_t src_pitch_blocks, const flo
   if (rc == TX_OK && bias_dev) {
     check(cudaMalloc(&h->bias, size_t(rows) * 2), "cudaMalloc(bias)");
     if (rc == TX_OK) check(cudaMemcpy(h->bias, bias_dev, size_t(rows) * 2, cudaMemcpyDeviceToDevice), "cudaMemcpy(bias)");
+    h->bias_dtype = bias_dtype;
   }
   if (rc == TX_OK) check(cudaDeviceSynchronize(), "pack synchronise");
   if (staging) cudaFree(staging);
@@ -179,9 +179,12 @@ int tx_linear(uint64_t handle, const void *x, void *y, int tokens, int dtype, vo
   Handle *h = as_handle(handle);
   if (!h) return fail(TX_EINVAL, "null Texelator handle");
   if (!x || !y) return fail(TX_EINVAL, "input must be contiguous CUDA FP16 or BF16");
-  if (dtype == TX_DTYPE_F16) return fail(TX_EUNSUPPORTED, "fp16 activations are not supported by this build (bf16 only)");
-  if (dtype != TX_DTYPE_BF16) return fail(TX_EINVAL, "input must be contiguous CUDA FP16 or BF16");
+  if (dtype != TX_DTYPE_BF16 && dtype != TX_DTYPE_F16) return fail(TX_EINVAL, "input must be contiguous CUDA FP16 or BF16");
   if (tokens <= 0) return fail(TX_EINVAL, "input shape/device mismatch");
+  if (h->bias && h->bias_dtype != dtype) return fail(TX_EINVAL, "input and bias dtypes must match");   // texelator_cuda.cu:1449
+  const bool half_io = dtype == TX_DTYPE_F16;
+  if (half_io && h->decode_path != TX_DECODE_ALU_MMA)
+    return fail(TX_EUNSUPPORTED, "the exact-arithmetic and texture decode paths restate the reference's bf16 kernel; fp16 runs on the default path");
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15)
     return fail(TX_EINVAL, "activation and output pointers must be 16-byte aligned");
   auto stream = static_cast<cudaStream_t>(stream_ptr);
@@ -193,22 +196,26 @@ int tx_linear(uint64_t handle, const void *x, void *y, int tokens, int dtype, vo
   int rc;
   // texelator_cuda.cu:1341 -- tokens >= threshold takes the prefill side of the dispatcher
   if (tokens >= h->prefill_threshold && h->prefill_backend >= 5 && prefill_tile_eligible(h, h->prefill_backend, tokens)) {
-    rc = launch_prefill_tile(h, h->prefill_backend, xb, yb, tokens, stream);
+    rc = launch_prefill_tile(h, h->prefill_backend, xb, yb, tokens, stream, half_io);
   } else if (h->decode_path == TX_DECODE_ALU_EXACT) {
     rc = launch_gemv_exact(h, xb, yb, tokens, stream);
   } else if (h->decode_path == TX_DECODE_TEXTURE && tokens < h->prefill_threshold) {
     rc = launch_gemv_texture(h, xb, yb, tokens, stream);
   } else {
-    rc = launch_gemv(h, xb, yb, tokens, stream);
+    rc = launch_gemv(h, xb, yb, tokens, stream, half_io);
   }
   if (current != h->device) cudaSetDevice(current);
   return rc;
 }
 
+// the entry points below read the bias as bf16
+static bool bias_is_bf16(const Handle *h) { return !h->bias || h->bias_dtype == TX_DTYPE_BF16; }
+
 int tx_linear_static_scratch(uint64_t handle, const void *x, void *y, int tokens, int dtype, void *stream_ptr) {
   Handle *h = as_handle(handle);
   if (!h) return fail(TX_EINVAL, "null Texelator handle");
   if (!x || !y || dtype != TX_DTYPE_BF16) return fail(TX_EINVAL, "input must be contiguous CUDA BF16");
+  if (!bias_is_bf16(h)) return fail(TX_EINVAL, "input and bias dtypes must match");
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15)
     return fail(TX_EINVAL, "activation and output pointers must be 16-byte aligned");
   int current = 0;
@@ -224,6 +231,7 @@ int tx_linear_single(uint64_t handle, const void *x, const void *staged, int swi
                      size_t partial_stride, void *stream_ptr) {
   Handle *h = as_handle(handle);
   if (!h) return fail(TX_EINVAL, "null Texelator handle");
+  if (!bias_is_bf16(h)) return fail(TX_EINVAL, "input and bias dtypes must match");
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(staged) | reinterpret_cast<uintptr_t>(y) |
        reinterpret_cast<uintptr_t>(y_partial)) & 15)
     return fail(TX_EINVAL, "activation and output pointers must be 16-byte aligned");
@@ -251,6 +259,7 @@ int tx_linear_fused(uint64_t handle, const void *x, const void *delta, const voi
   Handle *h = as_handle(handle);
   if (!h) return fail(TX_EINVAL, "null Texelator handle");
   if (!x || !y || dtype != TX_DTYPE_BF16) return fail(TX_EINVAL, "input must be contiguous CUDA BF16");
+  if (!bias_is_bf16(h)) return fail(TX_EINVAL, "input and bias dtypes must match");
   if (tokens < 1) return fail(TX_EINVAL, "tokens must be positive");
   if (h->decode_path != TX_DECODE_ALU_MMA) return fail(TX_EUNSUPPORTED, "fused linear runs on the ALU mma decode path only");
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(delta) |

@@ -1359,6 +1359,7 @@ int tx_linear_single_push(uint64_t handle, const void *x, const void *staged, vo
                           void *epoch_word, void *stream) {
   Handle *h = reinterpret_cast<Handle *>(handle);
   if (!h || h->magic != 0x54584234) return fail(TX_EINVAL, "null Texelator handle");
+  if (h->bias && h->bias_dtype != TX_DTYPE_BF16) return fail(TX_EINVAL, "input and bias dtypes must match");
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(staged)) & 15)
     return fail(TX_EINVAL, "activation pointers must be 16-byte aligned");
   PeerPush peers;

@@ -317,7 +317,7 @@ cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, siz
 int launch_retile(const uint8_t *rowmajor_dev, Handle *h, cudaStream_t stream);
 int launch_untile(const Handle *h, uint8_t *rowmajor_dev, cudaStream_t stream);
 int launch_dequant(const Handle *h, void *out, int what, cudaStream_t stream);
-int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
+int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream, bool half_io = false);
 int launch_gemv_fused(const Handle *h, const __nv_bfloat16 *x, const __nv_bfloat16 *delta, const __nv_bfloat16 *gamma, float eps,
                       __nv_bfloat16 *residual_out, bool swiglu, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 bool gemv_single_eligible(const Handle *h);
@@ -328,7 +328,7 @@ int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfl
 int launch_gemv_exact(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_gemv_texture(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_prefill_tile(const Handle *h, int backend, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens,
-                        cudaStream_t stream);
+                        cudaStream_t stream, bool half_io = false);
 bool prefill_tile_eligible(const Handle *h, int backend, int tokens);
 int gemv_kernel_info(int64_t out[9]);
 int prefill_kernel_info(int backend, int64_t out[9]);

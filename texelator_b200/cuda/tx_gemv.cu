@@ -50,7 +50,7 @@ struct GemvParams {
   const float *xmul;        // [T] 2^s * 65536/889 per token (PRE)
   int M, K, KI, T, MT;
   int KP;                   // KI * 128
-  int palette;              // TX_PALETTE_*
+  int palette;              // TX_PALETTE_* in the low byte; kHalfIO: bias and y are fp16 (the activations then come through xprep)
   // fused prologue (FUSE & 1): x is the residual stream; a = rmsnorm(bf16(x + delta)) * gamma feeds the linear
   const __nv_bfloat16 *delta;   // [T, K] or null
   const __nv_bfloat16 *gamma;   // [K]
@@ -68,18 +68,27 @@ struct SoloExtras {
   PeerPush push;                // world > 0: the bf16 result goes as packets into every rank's inbox
 };
 
+constexpr int kHalfIO = 0x100;   // flag in GemvParams::palette (a field of its own would grow the parameter block)
 constexpr int kFuseNorm = 1;     // residual add + RMSNorm in the activation staging
 constexpr int kFuseSwiglu = 2;   // rows are (gate, up) pairs: y[t, i] = silu(gate_i) * up_i
 
 // Pre-pass for larger token counts: one CTA per token writes scaled fp16 activations and the
-// per-token multiplier 2^s * 65536/889 to scratch.
-__global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ xprep,
+// per-token multiplier 2^s * 65536/889 to scratch.  fp16 activations (HALF) already are what the
+// tensor core takes: they are copied with the row padded to whole units, multiplier 65536/889.
+template <bool HALF>
+__global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const void *__restrict__ x, __half *__restrict__ xprep,
                                                                  float *__restrict__ xmul, int K, int KP) {
   __shared__ unsigned warp_max[kGemvWarps];
   grid_dependency_wait();
   int tok = blockIdx.x;
-  const uint4 *src = reinterpret_cast<const uint4 *>(x + size_t(tok) * K);
+  const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + size_t(tok) * K);
   int chunks = K / 8, padded = KP / 8;
+  if (HALF) {
+    if (threadIdx.x == 0) xmul[tok] = kNumeratorScale;
+    uint4 *copy = reinterpret_cast<uint4 *>(xprep + size_t(tok) * KP);
+    for (int i = threadIdx.x; i < padded; i += kGemvThreads) copy[i] = i < chunks ? __ldcg(src + i) : make_uint4(0, 0, 0, 0);
+    return;
+  }
   unsigned m = 0;
   for (int i = threadIdx.x; i < chunks; i += kGemvThreads) m = max(m, chunk_absmax(__ldcg(src + i)));
   m = __reduce_max_sync(0xffffffffu, m);
@@ -296,6 +305,7 @@ gemv_tile_kernel(const GemvParams p) {
       row_live[j] = ok;
       row_scale[j] = ok ? p.scales[row] : 0.f;
       row_bias[j] = ok && p.bias ? __bfloat162float(p.bias[row]) : 0.f;
+      if (PRE && (p.palette & kHalfIO) && ok && p.bias) row_bias[j] = __half2float(reinterpret_cast<const __half *>(p.bias)[row]);
       if (FUSE & kFuseSwiglu) {
         up_scale[j] = ok ? p.scales[row + 8] : 0.f;
         up_bias[j] = ok && p.bias ? __bfloat162float(p.bias[row + 8]) : 0.f;
@@ -324,7 +334,7 @@ gemv_tile_kernel(const GemvParams p) {
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
         unsigned aq[8], ar[8];
-        if (LOWMODE && p.palette == TX_PALETTE_HARDWARE) {   // uniform
+        if (LOWMODE && (p.palette & 0xff) == TX_PALETTE_HARDWARE) {   // uniform
           if (sub == 0) { decode_duo_first<true>(q, aq); decode_duo_first<true>(r, ar); }
           else { decode_duo_second<true>(q, aq); decode_duo_second<true>(r, ar); }
         } else {
@@ -332,8 +342,8 @@ gemv_tile_kernel(const GemvParams p) {
           else { decode_duo_second(q, aq); decode_duo_second(r, ar); }
         }
         if (LOWMODE && __any_sync(0xffffffffu, flag != 0)) {   // rare, warp-uniform: redo the low-mode blocks
-          if (duo_block_is_low(q, sub)) decode_block_slow(q, sub, aq, p.palette);
-          if (duo_block_is_low(r, sub)) decode_block_slow(r, sub, ar, p.palette);
+          if (duo_block_is_low(q, sub)) decode_block_slow(q, sub, aq, p.palette & 0xff);
+          if (duo_block_is_low(r, sub)) decode_block_slow(r, sub, ar, p.palette & 0xff);
         }
         if (NT == 1) {
           // One token tile: lanes whose token does not exist skip the load (their MMA columns are never
@@ -401,6 +411,8 @@ gemv_tile_kernel(const GemvParams p) {
               const float gate = __bfloat162float(__float2bfloat16(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j])));
               const float up = __bfloat162float(__float2bfloat16(fmaf(up_sum, up_scale[j] * tokmul[tok], up_bias[j])));
               p.y[size_t(tok) * (p.M / 2) + tile * 8 + (ln >> 2)] = __float2bfloat16(gate / (1.f + __expf(-gate)) * up);
+            } else if (PRE && (p.palette & kHalfIO)) {
+              reinterpret_cast<__half *>(p.y)[size_t(tok) * p.M + row] = __float2half_rn(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j]));
             } else {
               p.y[size_t(tok) * p.M + row] = __float2bfloat16(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j]));
             }
@@ -880,13 +892,13 @@ struct GemvPlan {
   size_t smem;
 };
 
-static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, bool single_token_kernel = false) {
+static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, bool single_token_kernel = false, bool force_pre = false) {
   Workspace *ws = workspace_for(h->device);
   if (!ws) return TX_ECUDA;
   int KP = h->KI * 128;
   plan.nt = token_tiles(tokens);
   // in-CTA activation conversion only while it stays a short prologue
-  plan.pre = !(tokens <= 2 && size_t(tokens) * h->K <= 36864);
+  plan.pre = force_pre || !(tokens <= 2 && size_t(tokens) * h->K <= 36864);
   if (fuse && plan.pre) return fail(TX_EINVAL, "fused linear handles at most 2 tokens with tokens * K <= 36864");
   // The single-token kernel (no per-weight arithmetic) is taken on request only (tx_linear_single): it
   // pays off when its token arrives staged; staging a bf16 row costs it more than the general kernel.
@@ -923,7 +935,10 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, 
   return TX_OK;
 }
 
-int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream) {
+// `half_io`: x, y and the handle's bias are fp16 (the reference's texelator_bc4_kernel,
+// texelator_cuda.cu:94-139, which multiplies the un-rounded pal*scale in fp32 -- what this kernel computes
+// for either type); the activations then always take the pre-pass, which for fp16 is a padded copy.
+int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream, bool half_io) {
   Workspace *ws = workspace_for(h->device);
   if (!ws) return TX_ECUDA;
   int KP = h->KI * 128;
@@ -932,7 +947,7 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
   for (int t0 = 0; t0 < tokens; t0 += per_pass) {
     int n = std::min(per_pass, tokens - t0);
     GemvPlan plan;
-    int rc = plan_gemv(h, n, plan);
+    int rc = plan_gemv(h, n, plan, 0, false, half_io);
     if (rc != TX_OK) return rc;
     GemvParams p{};
     p.tiles = reinterpret_cast<const uint4 *>(h->tiles);
@@ -947,11 +962,12 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
     p.MT = h->MT;
     p.T = n;
     p.KP = KP;
-    p.palette = h->palette;
+    p.palette = h->palette | (half_io ? kHalfIO : 0);
     if (plan.pre) {
       // scaled fp16 activations go through the per-device scratch (one pre-pass CTA per token)
       if (size_t(n) * KP > ws->xprep_halfs) return fail(TX_EINVAL, "tokens*K exceeds the activation scratch of the decode GEMV");
-      gemv_xprep_kernel<<<n, kGemvThreads, 0, stream>>>(p.x, ws->xprep, ws->xmul, h->K, KP);
+      if (half_io) gemv_xprep_kernel<true><<<n, kGemvThreads, 0, stream>>>(p.x, ws->xprep, ws->xmul, h->K, KP);
+      else gemv_xprep_kernel<false><<<n, kGemvThreads, 0, stream>>>(p.x, ws->xprep, ws->xmul, h->K, KP);
       count_launch();
       p.xprep = ws->xprep;
       p.xmul = ws->xmul;
@@ -1163,7 +1179,7 @@ int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfl
   p.palette = h->palette;
   p.xprep = scratch->activations;
   p.xmul = scratch->multipliers;
-  gemv_xprep_kernel<<<tokens, kGemvThreads, 0, stream>>>(x, scratch->activations, scratch->multipliers, h->K, KP);
+  gemv_xprep_kernel<false><<<tokens, kGemvThreads, 0, stream>>>(x, scratch->activations, scratch->multipliers, h->K, KP);
   count_launch();
   const int grid = std::max(1, std::min(h->MT, scratch->sm_count * std::min(per_sm, 3)));
   kernel<<<grid, kGemvThreads, smem, stream>>>(p);

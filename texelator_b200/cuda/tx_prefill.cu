@@ -83,6 +83,7 @@ struct PrefillParams {
   int *status;
   int M, K, KI, MT, T;
   int palette;
+  int half_io;   // bias and y are fp16 (the staged activations are fp16 either way)
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -159,7 +160,7 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned 
 constexpr int kStageThreads = 1024;
 __global__ void __launch_bounds__(kStageThreads) stage_activations_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ out,
                                                                           float *__restrict__ xmul, int K, int KP, int tokens,
-                                                                          int padded_tokens) {
+                                                                          int padded_tokens, int half_in) {
   __shared__ unsigned warp_max[32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = K / 8, padded = KP / 8;
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(kStageThreads) stage_activations_kernel(const 
   {
     const int tok = first + (warp >> 2);
     unsigned m = 0;
-    if (tok < tokens) {
+    if (tok < tokens && !half_in) {
       const uint4 *src = reinterpret_cast<const uint4 *>(x + size_t(tok) * K);
       for (int i = (warp & 3) * 32 + lane; i < chunks; i += 128) m = max(m, chunk_absmax(src[i]));
       m = __reduce_max_sync(0xffffffffu, m);
@@ -179,12 +180,13 @@ __global__ void __launch_bounds__(kStageThreads) stage_activations_kernel(const 
   const unsigned m = max(max(warp_max[4 * j], warp_max[4 * j + 1]), max(warp_max[4 * j + 2], warp_max[4 * j + 3]));
   float mult, inverse;
   token_scaling(m, mult, inverse);
+  if (half_in) inverse = 1.f;   // fp16 activations (x then points to fp16) are the operand as they are
   if (threadIdx.x < 8 && tok < tokens) xmul[tok] = inverse * kNumeratorScale;
   uint4 *dst = reinterpret_cast<uint4 *>(out);
   const uint4 *src = reinterpret_cast<const uint4 *>(x + size_t(tok < tokens ? tok : 0) * K);
   for (int chunk = threadIdx.x >> 3; chunk < padded; chunk += kStageThreads / 8)
     dst[size_t(chunk) * padded_tokens + tok] =
-        (tok < tokens && chunk < chunks) ? convert_chunk(src[chunk], mult) : make_uint4(0, 0, 0, 0);
+        (tok < tokens && chunk < chunks) ? (half_in ? src[chunk] : convert_chunk(src[chunk], mult)) : make_uint4(0, 0, 0, 0);
 }
 
 template <int MT, int BN, int BK>
@@ -354,7 +356,9 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
       for (int item = warp >> 2; item < MT * (BN / 32); item += kProducerWarps / 4) {
         const int m = item / (BN / 32), c = item % (BN / 32);
         const int row = row0 + m * kMmaM + quarter * 32 + lane;
-        const float bias = (row < p.M && p.bias) ? __bfloat162float(p.bias[row]) : 0.f;
+        const float bias = (row < p.M && p.bias)
+                               ? (p.half_io ? __half2float(reinterpret_cast<const __half *>(p.bias)[row]) : __bfloat162float(p.bias[row]))
+                               : 0.f;
         const float row_scale = row < p.M ? p.scales[row] : 0.f;
         unsigned v[32];
         tmem_load32(tmem_base + (unsigned(quarter * 32) << 16) + unsigned(m * BN + c * 32), v);
@@ -362,8 +366,11 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int tok = tok0 + c * 32 + j;
-            if (tok < p.T)
-              p.y[size_t(tok) * p.M + row] = __float2bfloat16(fmaf(__uint_as_float(v[j]), row_scale * __ldg(p.xmul + tok), bias));
+            if (tok < p.T) {
+              const float value = fmaf(__uint_as_float(v[j]), row_scale * __ldg(p.xmul + tok), bias);
+              if (p.half_io) reinterpret_cast<__half *>(p.y)[size_t(tok) * p.M + row] = __float2half_rn(value);
+              else p.y[size_t(tok) * p.M + row] = __float2bfloat16(value);
+            }
           }
         }
       }
@@ -418,7 +425,7 @@ bool prefill_tile_eligible(const Handle *h, int backend, int tokens) {
 }
 
 template <int MT, int BN, int BK>
-static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream) {
+static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream, bool half_io) {
   using Cfg = TileConfig<MT, BN, BK>;
   Workspace *ws = workspace_for(h->device);
   if (!ws) return TX_ECUDA;
@@ -440,7 +447,7 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
     const int n = std::min(capacity, tokens - t0);
     const int padded_tokens = (n + 31) & ~31;
     stage_activations_kernel<<<padded_tokens / 8, kStageThreads, 0, stream>>>(x + size_t(t0) * h->K, ws->xprep, ws->xmul, h->K, KP, n,
-                                                                    padded_tokens);
+                                                                    padded_tokens, half_io ? 1 : 0);
     count_launch();
     // staged X viewed as [KP/8 chunks][padded_tokens/32][32 tokens x 8 elements]: a box is BN/32 runs of
     // 512 contiguous bytes per chunk and lands as BN-token core-matrix columns
@@ -467,6 +474,7 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
     p.MT = h->MT;
     p.T = n;
     p.palette = h->palette;
+    p.half_io = half_io ? 1 : 0;
     dim3 grid((h->M + Cfg::rows - 1) / Cfg::rows, (n + BN - 1) / BN);
     prefill_umma_kernel<MT, BN, BK><<<grid, kPrefillThreads, Cfg::smem, stream>>>(p, map);
     count_launch();
@@ -475,13 +483,16 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
   return TX_OK;
 }
 
-int launch_prefill_tile(const Handle *h, int backend, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream) {
+// `half_io`: x, y and the handle's bias are fp16 (the reference multiplies fp16(pal*scale) with cuBLAS there,
+// texelator_cuda.cu:996-1046; this kernel multiplies the exact numerators and scales in the epilogue)
+int launch_prefill_tile(const Handle *h, int backend, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream,
+                        bool half_io) {
   switch (backend) {
-    case 5: return launch_tile<1, 256, 128>(h, x, y, tokens, stream);
-    case 6: return launch_tile<2, 256, 64>(h, x, y, tokens, stream);
-    case 7: return launch_tile<1, 128, 128>(h, x, y, tokens, stream);
-    case 8: return launch_tile<1, 64, 128>(h, x, y, tokens, stream);
-    case 9: return launch_tile<1, 192, 128>(h, x, y, tokens, stream);
+    case 5: return launch_tile<1, 256, 128>(h, x, y, tokens, stream, half_io);
+    case 6: return launch_tile<2, 256, 64>(h, x, y, tokens, stream, half_io);
+    case 7: return launch_tile<1, 128, 128>(h, x, y, tokens, stream, half_io);
+    case 8: return launch_tile<1, 64, 128>(h, x, y, tokens, stream, half_io);
+    case 9: return launch_tile<1, 192, 128>(h, x, y, tokens, stream, half_io);
     default: return fail(TX_EINVAL, "backend is not a tensor-core tile candidate");
   }
 }

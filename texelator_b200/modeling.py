@@ -292,7 +292,9 @@ class BC4Decoder:
         if not dense:
             return self.ext.linear(handle, x)
         _, w, bias = next(item for item in self.dense if item[0] == handle)
-        y = (x.float() @ w.float().T)
+        # dense=True: fp32 GEMM on the same bf16(pal*scale) matrix; dense="bf16": the library's bf16 GEMM (fp32
+        # accumulation in another order), which shows how far rounding alone moves a model's output
+        y = (x @ w.T).float() if dense == "bf16" else x.float() @ w.float().T
         return (y + bias.float() if bias is not None else y).to(x.dtype)
 
     def _reduce(self, t):

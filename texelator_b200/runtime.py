@@ -73,6 +73,7 @@ C_API = {
     "tx_linear_single": (_i32, [_u64, _vp, _vp, _i32, _vp, _vp, _i32, ctypes.c_size_t, _vp]),
     "tx_linear_single_info": (_i32, [_u64, _vp]),
     "tx_aux_add_rmsnorm_single": (_i32, [_vp, _vp, _vp, _i32, ctypes.c_size_t, _vp, _vp, _vp, _i32, ctypes.c_float, _vp]),
+    "tx_encode": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp]),
     "tx_linear_single_push": (_i32, [_u64, _vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "tx_aux_peer_reduce_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, ctypes.c_float, _vp, _i32, _vp, _vp]),
     "tx_aux_peer_best_token": (_i32, [_vp, _vp, ctypes.c_longlong, _vp, _i32, _i32, _vp, _vp, _vp]),
@@ -375,6 +376,22 @@ class _Extension:
     def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
         tokens, two_i = gate_up.shape
         self._check(self._lib.tx_aux_silu_mul(gate_up.data_ptr(), out.data_ptr(), tokens, two_i // 2, self._stream(gate_up)))
+
+    def encode(self, weight: torch.Tensor, hdiag: torch.Tensor, lut: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """The reference's E3 encoder (``encode_linear_e3``, texelator/encoder.py:120-157) on the GPU, byte-identical:
+        CUDA fp32 ``weight [M, K]``, ``hdiag [K]``, ``lut [255, 255, 8]`` -> (uint8 blocks ``[M*K/2]``, fp32 scales ``[M]``)."""
+        if not (weight.is_cuda and hdiag.is_cuda and lut.is_cuda) or weight.dim() != 2:
+            raise RuntimeError("encode needs CUDA tensors: weight [M, K], hdiag [K], lut [255, 255, 8]")
+        m, k = weight.shape
+        if hdiag.numel() != k or lut.numel() != 255 * 255 * 8:
+            raise RuntimeError("encode: hdiag must have K elements and lut 255*255*8")
+        weight, hdiag, lut = weight.float().contiguous(), hdiag.float().contiguous(), lut.float().contiguous()
+        blocks = torch.empty(m * k // 2, dtype=torch.uint8, device=weight.device)
+        scales = torch.empty(m, dtype=torch.float32, device=weight.device)
+        with torch.cuda.device(weight.device):
+            self._check(self._lib.tx_encode(weight.data_ptr(), hdiag.data_ptr(), lut.data_ptr(), m, k, blocks.data_ptr(),
+                                            scales.data_ptr(), self._stream(weight)))
+        return blocks, scales
 
     def linear_single_info(self, handle: int) -> tuple[bool, int, int]:
         """(eligible for the single-token kernel, suggested K splits, bytes of a staged token)."""
