@@ -199,8 +199,8 @@ def timed_steps(model, steps: int, warmup: int, world: int, e2e: bool) -> float:
     copies the input token id from pinned host memory and reads the produced token id back."""
     import torch.distributed as dist
     stream = model.stream
-    host_in = torch.zeros(1, dtype=torch.int64).pin_memory()
-    host_out = torch.zeros(1, dtype=torch.int64).pin_memory()
+    host_in = torch.zeros(model.tok.numel(), dtype=torch.int64).pin_memory()
+    host_out = torch.zeros(model.tok.numel(), dtype=torch.int64).pin_memory()
 
     def one():
         if e2e:
@@ -235,7 +235,8 @@ def timed_steps(model, steps: int, warmup: int, world: int, e2e: bool) -> float:
             dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
         # rewind the position so the KV window of the next measurement is the same
         model.pos.copy_(start_pos)
-        model.mask[..., int(start_pos.item()):] = False
+        if start_pos.numel() == 1:
+            model.mask[..., int(start_pos.item()):] = False
         stream.synchronize()
     return float(elapsed.item()) / steps
 
@@ -545,6 +546,103 @@ def run_gpu_arm(args, config) -> None:
         raise SystemExit(f"a device-side bounded wait ran out (status {kernel_status}): the measurement is invalid")
 
 
+def run_batched(args, config) -> None:
+    """`--batch B`: B sequences decode one token each per step (BASELINE configuration 5 when the model is the
+    70B-class one on 8 GPUs).  Every sequence gets a real prompt of `--prompt` tokens through the tensor-core
+    prefill and then seeded random cache rows up to `--context` positions; prints one JSON line (tokens of all
+    sequences per second, the linears' share measured alone, the weight bytes they stream)."""
+    import torch.distributed as dist
+    from texelator_b200.batched import BatchedBC4Decoder
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the BC4 operator has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    device = torch.device("cuda", local)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    context = max(args.context, args.prompt)
+    results = []
+    model = None
+    for batch in [int(v) for v in str(args.batch).split(",")]:
+        if model is not None:
+            model.graph = None
+            model.free()
+            del model
+            torch.cuda.empty_cache()
+        model = BatchedBC4Decoder(config, device, context + steps + 2 * warmup + 8, batch, seed=1234, tp_rank=rank, tp_world=world,
+                                  lookahead=args.lookahead)
+        kernels = {}
+        if args.batch_kernel == "tiles":
+            for handle in model.handles:
+                model.ext.set_prefill(handle, 16, 1024)
+        elif args.batch_kernel == "tuned":
+            kernels = model.tune_decode_kernel()
+        for sequence in range(batch):
+            ids = torch.randint(0, config.vocab, (args.prompt,), generator=torch.Generator().manual_seed(sequence))
+            model.prefill_sequence(sequence, ids)
+            model.tok[sequence] = int(ids[-1])
+            model.fill_context(sequence, args.prompt, context, seed=7)
+        model.capture()
+        with ClockSampler(local) as clocks:
+            ms = timed_steps(model, steps, warmup, world, e2e=False)
+        ms_e2e = timed_steps(model, steps, warmup, world, e2e=True)
+        # the four linears of every layer alone, same handles, same batch, in one graph
+        stream = model.stream
+        with torch.cuda.stream(stream):
+            def linears():
+                for layer in range(config.layers):
+                    model.ext.linear_out(model.h_qkv[layer], model.buf_x, model.buf_qkv)
+                    model.ext.linear_out(model.h_o[layer], model.buf_attn, model.buf_o)
+                    model.ext.linear_out(model.h_gu[layer], model.buf_x, model.buf_gu)
+                    model.ext.linear_out(model.h_down[layer], model.buf_act, model.buf_down)
+            linears()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                linears()
+            for _ in range(3):
+                graph.replay()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(stream)
+            for _ in range(8):
+                graph.replay()
+            end.record(stream)
+            stream.synchronize()
+            linear_ms = begin.elapsed_time(end) / 8
+        weight_bytes = config.bc4_bytes_per_token() / world
+        peak, source = measured_peaks()
+        status = torch.tensor([model.ext.kernel_status()], device=device)
+        if world > 1:
+            dist.all_reduce(status, op=dist.ReduceOp.MAX)
+        results.append({"batch": batch, "tokens_per_second": batch * 1000.0 / ms, "ms_per_step": ms,
+                        "e2e_tokens_per_second": batch * 1000.0 / ms_e2e, "linears_ms_per_step": linear_ms,
+                        "linears_GBps_per_gpu": weight_bytes / linear_ms / 1e6, "linears_frac_of_hbm": weight_bytes / linear_ms / 1e6 / peak,
+                        "launches_per_step": int(model.launches_per_step), "kernel_status": int(status.item()),
+                        "kernels": {k: {"kernel": v[0], "us": v[1], "candidates_us": v[2]} for k, v in kernels.items()},
+                        "clocks": clocks.summary()})
+    if rank == 0:
+        print(json.dumps({"metric": "bc4_batched_decode_tokens_per_second", "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+                          "dtype": "bf16", "data": "synthetic", "peak_source": source,
+                          "config": {"workload": f"{config.name} dense decoder, batched decode, {args.prompt}-token prompts + random cache rows up to "
+                                                 f"{context} positions per sequence", "model_shape": config.name, "parallelism": f"tp{world}",
+                                     "decode_kernel": args.batch_kernel, "lookahead": args.lookahead,
+                                     "allreduce": "none" if world == 1 else "nccl inside the captured graph"},
+                          "batches": results}), flush=True)
+    sys.stdout.flush()
+    bad = max(r["kernel_status"] for r in results)
+    if world > 1:
+        model.graph = None
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0 if bad == 0 else 4)
+    model.free()
+    if bad:
+        raise SystemExit(f"a device-side bounded wait ran out (status {bad}): the measurement is invalid")
+
+
 def run_micro(args) -> None:
     """Small single-kernel case for profilers: `--micro MxK[xT]` packs enough random BC4 matrices of that
     shape to exceed L2, runs the linear on each in turn (CUDA events) and prints one JSON line."""
@@ -562,27 +660,40 @@ def run_micro(args) -> None:
         handles.append(ext.pack_encoded_device(*encode_minmax_cuda(weight, lut)))
         ext.set_lookahead(handles[-1], args.lookahead)
         ext.set_prefill_backend(handles[-1], args.backend)
+        ext.set_prefill(handles[-1], args.threshold, 1024)
         ext.set_palette(handles[-1], args.palette)       # throughput only: the bytes are the same either way
         ext.set_decode_path(handles[-1], args.decode_path)
     x = torch.randn(tokens, k, device="cuda").bfloat16()
     y = torch.empty(tokens, m, device="cuda", dtype=torch.bfloat16)
-    for _ in range(max(args.warmup, 3)):
-        for h in handles:
-            ext.linear_out(h, x, y)
-    torch.cuda.synchronize()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.cudart().cudaProfilerStart()
-    begin.record()
-    for _ in range(args.steps):
-        for h in handles:
-            ext.linear_out(h, x, y)
-    end.record()
-    torch.cuda.synchronize()
-    torch.cuda.cudart().cudaProfilerStop()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        def sweep():
+            for h in handles:
+                ext.linear_out(h, x, y)
+        for _ in range(max(args.warmup, 3)):
+            sweep()
+        stream.synchronize()
+        before = ext.launch_count()
+        graph = torch.cuda.CUDAGraph()          # one graph over all copies: no host time between the launches
+        with torch.cuda.graph(graph, stream=stream):
+            sweep()
+        launches = ext.launch_count() - before
+        graph.replay()
+        stream.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.cudart().cudaProfilerStart()
+        begin.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        end.record(stream)
+        stream.synchronize()
+        torch.cuda.cudart().cudaProfilerStop()
     us = begin.elapsed_time(end) * 1000 / (args.steps * copies)
     bytes_per_call = m * k // 2 + 4 * m + 2 * tokens * (k + m)
     print(json.dumps({"micro": args.micro, "copies": copies, "us_per_call": us, "GBps": bytes_per_call / us / 1e3,
-                      "TFLOPs": 2.0 * tokens * m * k / us / 1e6, "note": "eager launches: host overhead included"}), flush=True)
+                      "TFLOPs": 2.0 * tokens * m * k / us / 1e6, "launches_per_call": launches / copies,
+                      "note": "all copies in one CUDA graph"}), flush=True)
     runtime.free(handles)
 
 
@@ -599,6 +710,12 @@ def main() -> None:
     parser.add_argument("--nccl-allreduce", action="store_true", help="tensor parallel: keep NCCL all-reduces (default: fused peer-memory exchange)")
     parser.add_argument("--skip-extras", action="store_true", help="only the decode measurement (no prefill sweep / cfg1 / parity / exchange timing)")
     parser.add_argument("--layers", type=int, default=0, help="override the layer count (profiling aid; not a bench result)")
+    parser.add_argument("--batch", default=None, help="batched decode: B or a comma list of B (one JSON line with an entry per B)")
+    parser.add_argument("--context", type=int, default=4096, help="--batch: cache positions per sequence before the timed steps")
+    parser.add_argument("--batch-kernel", default="tuned", choices=["tuned", "gemv", "tiles"],
+                        help="--batch: B >= 16 through the multi-token decode kernel (gemv), the tensor-core tile kernel (tiles), "
+                             "or whichever measures faster per projection (tuned)")
+    parser.add_argument("--threshold", type=int, default=16, help="--micro: prefill threshold (token counts below it take the decode kernel)")
     parser.add_argument("--micro", default=None, help="MxK[xT]: time one linear shape alone (profiling aid)")
     parser.add_argument("--backend", type=int, default=5, help="prefill backend id for --micro with T >= 16")
     parser.add_argument("--decode-path", type=int, default=0, help="--micro: 0 mma.sync ALU decode, 1 exact ALU, 2 texture")
@@ -614,6 +731,10 @@ def main() -> None:
         config = dataclasses.replace(config, layers=args.layers, name=f"{config.name}-{args.layers}layers")
     if args.impl == "reference":
         run_reference_arm(args, config)
+    elif args.batch:
+        if args.prompt == 2048:
+            args.prompt = 512          # configuration 5's prompt length
+        run_batched(args, config)
     else:
         world = int(os.environ.get("WORLD_SIZE", "1"))
         if args.gpus != world:

@@ -84,8 +84,9 @@ int tx_pack_encoded_shard(const uint8_t *blocks, size_t nbytes, const float *sca
  * fp16 activations are the tensor-core operand as they are. */
 int tx_linear(uint64_t handle, const void *x, void *y, int tokens, int dtype, void *stream);
 
-/* No counterpart in the reference.  Same result as tx_linear for a small token group (1..32 tokens,
- * tokens * K <= 262144 with K rounded up to 128, one shared-memory pass), but the fp16 activation
+/* No counterpart in the reference.  The result of tx_linear for a small token group (1..32 tokens,
+ * tokens * K <= 262144 with K rounded up to 128, one shared-memory pass; every CTA sums whole rows here, while
+ * tx_linear may cut K into ranges, so the two can differ in the last bit of an output), but the fp16 activation
  * scratch of the multi-token decode kernel is a fixed array inside the library image instead of
  * memory from cudaMalloc, and the call allocates nothing on the device.  Meant for hosts that cannot
  * allocate when they need the linear (all memory owned by their own pool, a thread that must
@@ -254,6 +255,18 @@ int tx_aux_attention_step(const void *qkv, const float *cos_table, const float *
                           void *v_cache, float *scratch, void *out, int q_heads, int kv_heads, int head_dim, int max_len,
                           float scale, void *stream);
 int tx_aux_silu_mul(const void *gate_up, void *out, int tokens, int intermediate, void *stream);
+/* Batched decode (one token of each of `sequences` sequences per step; no reference counterpart, the reference
+ * serves a batch as tokens of one GEMV launch, texelator_cuda.cu:1438-1468, and leaves attention to PyTorch).
+ *   attention_step_batch : attention_step for every sequence in one launch.  qkv [sequences, (q_heads + 2 kv_heads) *
+ *                          head_dim], positions int64 [sequences], caches [sequences, kv_heads, max_len, head_dim],
+ *                          out [sequences, q_heads * head_dim]; `scratch` holds `sequences` times the floats of
+ *                          attention_step; sequences * kv_heads <= 4096.
+ *   silu_mul_pairs       : silu_mul for gate/up rows stored as alternating groups of eight (the row order the
+ *                          SwiGLU-fused linear takes): out[t, 8j + e] = silu(gu[t, 16j + e]) * gu[t, 16j + 8 + e]. */
+int tx_aux_attention_step_batch(const void *qkv, const float *cos_table, const float *sin_table, const void *positions, void *k_cache,
+                                void *v_cache, float *scratch, void *out, int sequences, int q_heads, int kv_heads, int head_dim,
+                                int max_len, float scale, void *stream);
+int tx_aux_silu_mul_pairs(const void *gate_up, void *out, int tokens, int intermediate, void *stream);
 
 /* Number of this library's kernels launched by the calling process since load (all threads). */
 int64_t tx_launch_count(void);

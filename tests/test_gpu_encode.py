@@ -83,3 +83,33 @@ def test_gpu_encoder_feeds_the_operator(ext, lut):
         assert weighted_error(blocks.cpu().numpy(), scales.cpu().numpy()) <= weighted_error(start_blocks, start_scales)
     finally:
         ext.free(handle)
+
+
+def test_directory_written_by_the_reference_loads_and_runs(ext, lut, golden_dir):
+    """The fixture directory written by the reference's encode_linear_e3 goes through ``pack_entry_handles``
+    unchanged (bias attached like ``runtime.install`` does), multiplies like the oracle says, unpacks to the
+    file's bytes, and the GPU encoder reproduces the files from the recorded fp32 inputs."""
+    import json
+    from texelator_b200 import runtime
+    root = golden_dir / "reference_artifact"
+    metadata = json.loads((root / "weights" / "metadata.json").read_text())
+    inputs = np.load(root / "inputs.npz")
+    rng = np.random.default_rng(11)
+    for entry in metadata["entries"]:
+        key = entry["artifact_key"]
+        blocks = np.fromfile(root / "weights" / entry["blocks_file"], dtype=np.uint8)
+        scales = np.fromfile(root / "weights" / entry["scales_file"], dtype="<f4")
+        bias = torch.from_numpy(inputs[f"{key}/bias"]).bfloat16().cuda() if entry["bias"] else None
+        handles = runtime.pack_entry_handles(root / "weights", entry, bias=bias, lookahead=2)
+        try:
+            assert len(handles) == 1 and ext.handle_info(handles[0])[:2] == [entry["M"], entry["K"]]
+            assert np.array_equal(ext.unpack_blocks(handles[0]).numpy(), blocks)
+            x = torch.from_numpy(rng.standard_normal((3, entry["K"])).astype(np.float32)).bfloat16()
+            y = ext.linear(handles[0], x.cuda()).float().cpu().numpy()
+            ref = O.linear_bf16(x.float().numpy(), blocks, scales, lut, None if bias is None else bias.float().cpu().numpy())
+            assert O.rel_rms(y, ref) <= 1e-2
+        finally:
+            runtime.free(handles)
+        got_blocks, got_scales = ext.encode(torch.from_numpy(inputs[f"{key}/weight"]).cuda(), torch.from_numpy(inputs[f"{key}/hdiag"]).cuda(),
+                                            torch.from_numpy(lut).cuda())
+        assert np.array_equal(got_blocks.cpu().numpy(), blocks) and np.array_equal(got_scales.cpu().numpy(), scales)

@@ -127,3 +127,26 @@ def test_model_config_byte_counts():
     assert CONFIGS["27b-class"].bc4_bytes_per_token() == 10583015424      # 10.583 GB per decoded token
     assert abs(CONFIGS["qwen2.5-3b-shaped"].bc4_bytes_per_token() / 1e9 - 1.391) < 0.002
     assert abs(CONFIGS["70b-class"].bc4_bytes_per_token() / 1e9 - 34.252) < 0.002
+
+
+def test_directory_written_by_the_reference_is_read_unchanged(golden_dir, lut):
+    """``reference_artifact/`` was written by the reference's own discover_linears / encode_linear_e3 / write_json
+    (tests/golden/make_artifact.py): its checksums validate, its entries carry the fields this build writes, and
+    the restated encoder reproduces its files byte for byte from the recorded inputs."""
+    import json
+    from oracle import bc4_oracle as O
+    from texelator_b200 import artifacts
+    root = golden_dir / "reference_artifact"
+    validation = artifacts.validate_encoded(root / "weights")
+    assert validation["ok"] and validation["entries"] == 3
+    metadata = json.loads((root / "weights" / "metadata.json").read_text())
+    assert metadata["palette_sha256"] == O.palette_sha256(lut)
+    inputs = np.load(root / "inputs.npz")
+    for entry in metadata["entries"]:
+        assert entry["artifact_key"] == artifacts.artifact_key(entry["module_name"])
+        blocks = np.fromfile(root / "weights" / entry["blocks_file"], dtype=np.uint8)
+        scales = np.fromfile(root / "weights" / entry["scales_file"], dtype="<f4")
+        assert blocks.size == entry["M"] * entry["K"] // 2 == entry["blocks_bytes"] and scales.size == entry["M"]
+        key = entry["artifact_key"]
+        again_blocks, again_scales = O.encode_linear(inputs[f"{key}/weight"], inputs[f"{key}/hdiag"], lut)
+        assert np.array_equal(again_blocks, blocks) and np.array_equal(again_scales, scales)

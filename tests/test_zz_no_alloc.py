@@ -28,9 +28,10 @@ def test_static_scratch_linear_matches_regular_linear(lut):
             expected = ext.linear(handle, x)
             got = ext.linear_static_scratch(handle, x)
             torch.cuda.synchronize()
-            # same kernels, same arithmetic order: the test-suite's GEMV tolerance (rel-RMS <= 1e-2) is met exactly
-            assert O.rel_rms(got.float().cpu().numpy(), expected.float().cpu().numpy()) <= 1e-2
-            assert torch.equal(got, expected)
+            # same kernel and arithmetic; tx_linear may cut K into ranges per CTA where this entry point sums whole
+            # rows, so single outputs can land on the neighbouring bf16 value (2^-8 relative)
+            assert O.rel_rms(got.float().cpu().numpy(), expected.float().cpu().numpy()) <= 3e-3
+            assert torch.equal(got, ext.linear_static_scratch(handle, x))          # and it repeats itself bit for bit
             ref = O.linear_bf16(x.float().cpu().numpy(), blocks, scales, lut, bias=bias.float().cpu().numpy())
             assert O.rel_rms(got.float().cpu().numpy(), ref) <= 1e-2
         with pytest.raises(RuntimeError, match="1..32 tokens"):

@@ -35,7 +35,7 @@ bool pdl_enabled() {
 
 // The scratch is sized once per device: 48 Mi scaled fp16 activations (96 MiB; multi-token decode
 // passes use the first 32 tokens' worth, the prefill GEMM stages whole token chunks) plus one
-// multiplier per staged token.
+// multiplier per staged token, and 16 Mi floats (64 MiB) for the K-range sums of multi-token decode passes.
 Workspace *workspace_for(int device) {
   std::lock_guard<std::mutex> lock(g_workspace_guard);
   auto found = g_workspaces.find(device);
@@ -48,6 +48,8 @@ Workspace *workspace_for(int device) {
   ws.xprep_halfs = size_t(48) << 20;
   if (status == cudaSuccess) status = cudaMalloc(&ws.xprep, ws.xprep_halfs * sizeof(__half));
   if (status == cudaSuccess) status = cudaMalloc(&ws.xmul, 65536 * sizeof(float));
+  ws.partial_floats = size_t(16) << 20;
+  if (status == cudaSuccess) status = cudaMalloc(&ws.partial, ws.partial_floats * sizeof(float));
   if (status == cudaSuccess) status = cudaMalloc(&ws.status, 2 * sizeof(int));   // [0] kernel status, [1] pack-time scratch
   if (status == cudaSuccess) status = cudaMemset(ws.status, 0, 2 * sizeof(int));
   cudaSetDevice(previous);

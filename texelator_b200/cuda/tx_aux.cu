@@ -702,7 +702,8 @@ constexpr int kStepThreads = 256;
 constexpr int kStepRow = kHeadDim + 4;          // floats per (head, split) record: output, max, sum, pad
 constexpr int kStepMaxSplits = 256;
 constexpr int kStepMaxKvHeads = 128;
-__device__ unsigned g_attention_arrivals[kStepMaxKvHeads];
+constexpr int kStepMaxSlots = 4096;             // (sequence, kv head) pairs of one launch
+__device__ unsigned g_attention_arrivals[kStepMaxSlots];
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4 &raw, float (&out)[8]) {
   const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -730,6 +731,14 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_kernel(const _
   __shared__ int last_s;
   constexpr int kHalf = kHeadDim / 2, kWarps = kStepThreads / 32;
   const int split = blockIdx.x, kvh = blockIdx.y;
+  // batched step: blockIdx.z is the sequence; every array is [sequences][the one-sequence extent]
+  const int arrival_slot = int(blockIdx.z) * kv_heads + kvh;
+  qkv += size_t(blockIdx.z) * size_t(q_heads + 2 * kv_heads) * kHeadDim;
+  position += blockIdx.z;
+  k_cache += size_t(blockIdx.z) * kv_heads * max_len * kHeadDim;
+  v_cache += size_t(blockIdx.z) * kv_heads * max_len * kHeadDim;
+  partial += size_t(blockIdx.z) * q_heads * split_capacity * kStepRow;
+  out += size_t(blockIdx.z) * q_heads * kHeadDim;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   grid_launch_dependents();
   grid_dependency_wait();
@@ -868,10 +877,10 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_kernel(const _
   __syncthreads();
   if (tid == 0) {
     __threadfence();
-    const unsigned before = atomicAdd(&g_attention_arrivals[kvh], 1u);
+    const unsigned before = atomicAdd(&g_attention_arrivals[arrival_slot], 1u);
     last_s = before == unsigned(live - 1);
     if (last_s) {
-      g_attention_arrivals[kvh] = 0;      // every CTA of this launch has arrived: ready for the next launch
+      g_attention_arrivals[arrival_slot] = 0;      // every CTA of this launch has arrived: ready for the next launch
       __threadfence();
     }
   }
@@ -950,6 +959,14 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_loop_kernel(co
   __shared__ int last_s;
   constexpr int kHalf = kHeadDim / 2, kWarps = kStepThreads / 32;
   const int split = blockIdx.x, kvh = blockIdx.y;
+  // batched step: blockIdx.z is the sequence; every array is [sequences][the one-sequence extent]
+  const int arrival_slot = int(blockIdx.z) * kv_heads + kvh;
+  qkv += size_t(blockIdx.z) * size_t(q_heads + 2 * kv_heads) * kHeadDim;
+  position += blockIdx.z;
+  k_cache += size_t(blockIdx.z) * kv_heads * max_len * kHeadDim;
+  v_cache += size_t(blockIdx.z) * kv_heads * max_len * kHeadDim;
+  partial += size_t(blockIdx.z) * q_heads * split_capacity * kStepRow;
+  out += size_t(blockIdx.z) * q_heads * kHeadDim;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   grid_launch_dependents();
   grid_dependency_wait();
@@ -1121,10 +1138,10 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_loop_kernel(co
   __syncthreads();
   if (tid == 0) {
     __threadfence();
-    const unsigned before = atomicAdd(&g_attention_arrivals[kvh], 1u);
+    const unsigned before = atomicAdd(&g_attention_arrivals[arrival_slot], 1u);
     last_s = before == unsigned(live - 1);
     if (last_s) {
-      g_attention_arrivals[kvh] = 0;      // every CTA of this launch has arrived: ready for the next launch
+      g_attention_arrivals[arrival_slot] = 0;      // every CTA of this launch has arrived: ready for the next launch
       __threadfence();
     }
   }
@@ -1199,14 +1216,37 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16 *__re
   }
 }
 
+// the same for rows stored as (gate, up) groups of eight -- the row order of the SwiGLU-fused linear:
+// out[t, 8j + e] = silu(gu[t, 16j + e]) * gu[t, 16j + 8 + e]
+__global__ void __launch_bounds__(256) silu_mul_pairs_kernel(const __nv_bfloat16 *__restrict__ gu, __nv_bfloat16 *__restrict__ out,
+                                                             int inter, int tokens) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int chunks = inter / 8;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < size_t(tokens) * chunks; i += size_t(gridDim.x) * blockDim.x) {
+    const int t = int(i / chunks), j = int(i % chunks);
+    const uint4 *src = reinterpret_cast<const uint4 *>(gu + size_t(t) * 2 * inter + size_t(j) * 16);
+    const uint4 gate = __ldcg(src), up = __ldcg(src + 1);
+    const __nv_bfloat162 *pg = reinterpret_cast<const __nv_bfloat162 *>(&gate), *pu = reinterpret_cast<const __nv_bfloat162 *>(&up);
+    uint4 result;
+    __nv_bfloat162 *pr = reinterpret_cast<__nv_bfloat162 *>(&result);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 g = __bfloat1622float2(pg[e]), u = __bfloat1622float2(pu[e]);
+      pr[e] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4 *>(out + size_t(t) * inter + size_t(j) * 8) = result;
+  }
+}
+
 template <int GROUP, bool LOOP>
-static cudaError_t launch_attention_step(int splits, int kv_heads, cudaStream_t s, const __nv_bfloat16 *qkv, const float *cos_table,
+static cudaError_t launch_attention_step(int splits, int kv_heads, int sequences, cudaStream_t s, const __nv_bfloat16 *qkv, const float *cos_table,
                                          const float *sin_table, const long long *position, __nv_bfloat16 *k_cache,
                                          __nv_bfloat16 *v_cache, float *scratch, __nv_bfloat16 *out, int q_heads, int max_len, float scale) {
   if (LOOP)
-    return launch_pdl(attention_step_loop_kernel<GROUP>, dim3(splits, kv_heads), dim3(kStepThreads), 0, s, qkv, cos_table, sin_table, position,
+    return launch_pdl(attention_step_loop_kernel<GROUP>, dim3(splits, kv_heads, sequences), dim3(kStepThreads), 0, s, qkv, cos_table, sin_table, position,
                       k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale);
-  return launch_pdl(attention_step_kernel<GROUP>, dim3(splits, kv_heads), dim3(kStepThreads), 0, s, qkv, cos_table, sin_table, position,
+  return launch_pdl(attention_step_kernel<GROUP>, dim3(splits, kv_heads, sequences), dim3(kStepThreads), 0, s, qkv, cos_table, sin_table, position,
                     k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale);
 }
 
@@ -1406,19 +1446,21 @@ int tx_aux_attention_decode(const void *qkv, const void *k_cache, const void *v_
   return TX_OK;
 }
 
-int tx_aux_attention_step(const void *qkv, const float *cos_table, const float *sin_table, const void *position, void *k_cache,
-                          void *v_cache, float *scratch, void *out, int q_heads, int kv_heads, int head_dim, int max_len,
-                          float scale, void *stream) {
+static int attention_step_any(const void *qkv, const float *cos_table, const float *sin_table, const void *position, void *k_cache,
+                              void *v_cache, float *scratch, void *out, int sequences, int q_heads, int kv_heads, int head_dim,
+                              int max_len, float scale, void *stream) {
   if (!qkv || !cos_table || !sin_table || !position || !k_cache || !v_cache || !scratch || !out)
     return fail(TX_EINVAL, "tx_aux_attention_step: null argument");
-  if (head_dim != kHeadDim || kv_heads < 1 || kv_heads > kStepMaxKvHeads || q_heads % kv_heads || q_heads / kv_heads > kMaxGroup)
-    return fail(TX_EUNSUPPORTED, "tx_aux_attention_step supports head_dim 128, up to 128 kv heads and up to 8 query heads per kv head");
+  if (head_dim != kHeadDim || kv_heads < 1 || kv_heads > kStepMaxKvHeads || sequences < 1 || sequences * kv_heads > kStepMaxSlots ||
+      q_heads % kv_heads || q_heads / kv_heads > kMaxGroup)
+    return fail(TX_EUNSUPPORTED, "tx_aux_attention_step supports head_dim 128, up to 128 kv heads, up to 4096 (sequence, kv head) pairs and "
+                                 "up to 8 query heads per kv head");
   if (max_len < 1) return fail(TX_EINVAL, "tx_aux_attention_step: max_len must be positive");
   // one CTA per 64-key chunk while that fits two resident CTAs per SM; longer caches give every CTA several chunks
   int device = 0;
   TX_CUDA(cudaGetDevice(&device));
   Workspace *ws = workspace_for(device);
-  const int resident = std::max(1, (ws ? 2 * ws->sm_count : 256) / kv_heads);
+  const int resident = std::max(1, (ws ? 2 * ws->sm_count : 256) / (kv_heads * sequences));
   const int chunks_max = (max_len + kStepKeys - 1) / kStepKeys;
   // up to two waves of one-chunk CTAs (most of them idle while the cache is short) run the leaner variant
   const bool loop = chunks_max > 2 * resident || chunks_max > kStepMaxSplits;
@@ -1432,16 +1474,41 @@ int tx_aux_attention_step(const void *qkv, const float *cos_table, const float *
   switch (q_heads / kv_heads) {
 #define TX_STEP_CASE(G)                                                                                                          \
   case G:                                                                                                                        \
-    err = loop ? launch_attention_step<G, true>(splits, kv_heads, s, q, cos_table, sin_table, pos, kc, vc, scratch, o, q_heads,  \
-                                                max_len, scale)                                                                  \
-               : launch_attention_step<G, false>(splits, kv_heads, s, q, cos_table, sin_table, pos, kc, vc, scratch, o, q_heads, \
-                                                 max_len, scale);                                                                \
+    err = loop ? launch_attention_step<G, true>(splits, kv_heads, sequences, s, q, cos_table, sin_table, pos, kc, vc, scratch, o, \
+                                                q_heads, max_len, scale)                                                          \
+               : launch_attention_step<G, false>(splits, kv_heads, sequences, s, q, cos_table, sin_table, pos, kc, vc, scratch,   \
+                                                 o, q_heads, max_len, scale);                                                     \
     break;
     TX_STEP_CASE(1) TX_STEP_CASE(2) TX_STEP_CASE(3) TX_STEP_CASE(4) TX_STEP_CASE(5) TX_STEP_CASE(6) TX_STEP_CASE(7) TX_STEP_CASE(8)
 #undef TX_STEP_CASE
     default: return fail(TX_EUNSUPPORTED, "tx_aux_attention_step: unsupported query group");
   }
   TX_CUDA(err);
+  count_launch();
+  TX_CUDA(cudaGetLastError());
+  return TX_OK;
+}
+
+int tx_aux_attention_step(const void *qkv, const float *cos_table, const float *sin_table, const void *position, void *k_cache,
+                          void *v_cache, float *scratch, void *out, int q_heads, int kv_heads, int head_dim, int max_len,
+                          float scale, void *stream) {
+  return attention_step_any(qkv, cos_table, sin_table, position, k_cache, v_cache, scratch, out, 1, q_heads, kv_heads, head_dim, max_len,
+                            scale, stream);
+}
+
+int tx_aux_attention_step_batch(const void *qkv, const float *cos_table, const float *sin_table, const void *positions, void *k_cache,
+                                void *v_cache, float *scratch, void *out, int sequences, int q_heads, int kv_heads, int head_dim,
+                                int max_len, float scale, void *stream) {
+  return attention_step_any(qkv, cos_table, sin_table, positions, k_cache, v_cache, scratch, out, sequences, q_heads, kv_heads, head_dim,
+                            max_len, scale, stream);
+}
+
+int tx_aux_silu_mul_pairs(const void *gate_up, void *out, int tokens, int intermediate, void *stream) {
+  if (!gate_up || !out || tokens < 1 || intermediate < 8 || intermediate % 8) return fail(TX_EINVAL, "tx_aux_silu_mul_pairs: bad argument");
+  size_t chunks = size_t(tokens) * intermediate / 8;
+  int grid = int(std::min<size_t>((chunks + 255) / 256, 148 * 8));
+  TX_CUDA(launch_pdl(silu_mul_pairs_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                     static_cast<const __nv_bfloat16 *>(gate_up), static_cast<__nv_bfloat16 *>(out), intermediate, tokens));
   count_launch();
   TX_CUDA(cudaGetLastError());
   return TX_OK;

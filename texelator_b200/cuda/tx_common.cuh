@@ -163,6 +163,8 @@ struct Workspace {
   __half *xprep = nullptr;        // scaled fp16 activations of multi-token decode passes
   size_t xprep_halfs = 0;
   float *xmul = nullptr;          // per-token multipliers, one per staged token
+  float *partial = nullptr;       // fp32 sums of the K ranges of a multi-token decode pass, [splits][tokens][M]
+  size_t partial_floats = 0;
   int *status = nullptr;          // first non-zero code a kernel recorded when a bounded wait ran out
   int sm_count = 0;
 };
@@ -329,6 +331,9 @@ int launch_gemv_exact(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y,
 int launch_gemv_texture(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream);
 int launch_prefill_tile(const Handle *h, int backend, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens,
                         cudaStream_t stream, bool half_io = false);
+// y = round(sum of `ranges` fp32 partial results [ranges][tokens][M] + bias): second step of a launch that cut K
+int launch_combine(const float *partial, int ranges, const void *bias, void *y, int tokens, int M, bool half_io, int sm_count,
+                   cudaStream_t stream);
 bool prefill_tile_eligible(const Handle *h, int backend, int tokens);
 int gemv_kernel_info(int64_t out[9]);
 int prefill_kernel_info(int backend, int64_t out[9]);

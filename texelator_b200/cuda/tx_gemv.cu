@@ -52,10 +52,19 @@ struct GemvParams {
   int KP;                   // KI * 128
   int palette;              // TX_PALETTE_* in the low byte; kHalfIO: bias and y are fp16 (the activations then come through xprep)
   // fused prologue (FUSE & 1): x is the residual stream; a = rmsnorm(bf16(x + delta)) * gamma feeds the linear
-  const __nv_bfloat16 *delta;   // [T, K] or null
+  // The pre-pass variants (PRE) have no fused prologue and reuse two of its fields (the parameter block stays
+  // at its size): K is cut into `splits` ranges, CTA c takes range c % splits of row tiles c / splits, ... and
+  // stages only its range of the activations; with splits > 1 the scaled fp32 sums go to partial[split][T][M].
+  union {
+    const __nv_bfloat16 *delta;   // [T, K] or null
+    float *partial;
+  };
   const __nv_bfloat16 *gamma;   // [K]
   __nv_bfloat16 *residual_out;  // [T, K] or null: receives bf16(x + delta); must not alias x
-  float eps;
+  union {
+    float eps;
+    int splits;
+  };
 };
 
 // extras of the single-token kernel (kept out of GemvParams: the general kernel measured 4 % slower with
@@ -126,23 +135,29 @@ gemv_tile_kernel(const GemvParams p) {
   uint8_t *xs_g = smem_raw + kSmallBytes + kPartBytes;
   const unsigned zero_s = sbase + 256;
   const unsigned xs_s = sbase + kSmallBytes + kPartBytes;
-  const unsigned xs_stride = unsigned(p.KP) * 2 + kXsPad;
 
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // same value, but known to be warp-uniform
   const int g = lane >> 2, t = lane & 3;
   const int KI = p.KI, MT = p.MT;
-  const int WS = KI < kGemvWarps ? KI : kGemvWarps;   // warps that own column units
+  // this CTA's range of column units [kbeg, kbeg + KR) and its first row tile (the whole row without PRE)
+  const int S = PRE ? p.splits : 1;
+  const int split = PRE ? int(blockIdx.x) % S : 0;
+  const int kbeg = PRE ? split * KI / S : 0;
+  const int KR = PRE ? (split + 1) * KI / S - kbeg : KI;
+  const int tile0 = PRE ? int(blockIdx.x) / S : int(blockIdx.x);
+  const int tile_stride = PRE ? int(gridDim.x) / S : int(gridDim.x);
+  const unsigned xs_stride = (PRE ? unsigned((KI + S - 1) / S) * 256 : unsigned(p.KP) * 2) + kXsPad;
+  const int WS = KR < kGemvWarps ? KR : kGemvWarps;   // warps that own column units
   const bool worker = warp < WS;
-  const int per_tile = worker ? (KI - warp + WS - 1) / WS : 0;   // units of this warp in every tile
+  const int per_tile = worker ? (KR - warp + WS - 1) / WS : 0;   // units of this warp in every tile
 
   // -- first loads, issued before anything else.  The prefetch pointer walks this warp's units
-  //    (ki = warp, warp + WS, ... of tiles blockIdx.x, + gridDim.x, ...) and stops at the end of the payload.
-  const int tile_stride = gridDim.x;
+  //    (ki = kbeg + warp, + WS, ... of tiles tile0, + tile_stride, ...) and stops at the end of the payload.
   // The walk is kept as a 32-bit unit index (payloads stay far below 2^32 units) and stops loading at the
   // end of the payload.
   const unsigned unit_limit = unsigned(MT) * unsigned(KI);
-  unsigned unext = unsigned(blockIdx.x) * unsigned(KI) + unsigned(warp);
+  unsigned unext = unsigned(tile0) * unsigned(KI) + unsigned(kbeg + warp);
   const unsigned step_unit = WS, step_tile = unsigned(tile_stride) * unsigned(KI) - unsigned(per_tile - 1) * unsigned(WS);
   int pcount = 0;
   uint4 pend[LOOKAHEAD][2];
@@ -170,10 +185,11 @@ gemv_tile_kernel(const GemvParams p) {
   // -- activations -> fp16 in shared memory
   const int chunks = p.K / 8, padded = p.KP / 8;
   if (PRE) {
+    const int range_chunks = KR * 16;
     for (int tok = 0; tok < p.T; ++tok) {
-      const uint4 *xp = reinterpret_cast<const uint4 *>(p.xprep + size_t(tok) * p.KP);
+      const uint4 *xp = reinterpret_cast<const uint4 *>(p.xprep + size_t(tok) * p.KP) + kbeg * 16;
       uint4 *dst = reinterpret_cast<uint4 *>(xs_g + size_t(tok) * xs_stride);
-      for (int i = tid; i < padded; i += kGemvThreads) dst[i] = __ldcg(xp + i);
+      for (int i = tid; i < range_chunks; i += kGemvThreads) dst[i] = __ldcg(xp + i);
     }
     if (tid < p.T) tokmul[tid] = __ldcg(p.xmul + tid);
   } else {
@@ -273,7 +289,7 @@ gemv_tile_kernel(const GemvParams p) {
     }
   }
   __syncthreads();
-  if (!worker || int(blockIdx.x) >= MT) return;
+  if (!worker || tile0 >= MT) return;
 
   // shared address of this lane's activations per token tile (token = 8*nt + g); lanes whose token
   // does not exist read a block of zeros instead and never advance
@@ -321,7 +337,7 @@ gemv_tile_kernel(const GemvParams p) {
     for (int q = 0; q < 4; ++q) acc[nt][q] = acc2[nt][q] = 0.f;
 
   uint4 bsolo[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};   // B fragments of the NT == 1 path
-  int tile = blockIdx.x, done = 0, buf = 0;
+  int tile = tile0, done = 0, buf = 0;
   unsigned xoff = unsigned(warp) * 256;
   const unsigned xoff_step = unsigned(WS) * 256;
   load_row_constants(tile);
@@ -411,6 +427,8 @@ gemv_tile_kernel(const GemvParams p) {
               const float gate = __bfloat162float(__float2bfloat16(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j])));
               const float up = __bfloat162float(__float2bfloat16(fmaf(up_sum, up_scale[j] * tokmul[tok], up_bias[j])));
               p.y[size_t(tok) * (p.M / 2) + tile * 8 + (ln >> 2)] = __float2bfloat16(gate / (1.f + __expf(-gate)) * up);
+            } else if (PRE && S > 1) {
+              p.partial[(size_t(split) * p.T + tok) * p.M + row] = sum * (row_scale[j] * tokmul[tok]);
             } else if (PRE && (p.palette & kHalfIO)) {
               reinterpret_cast<__half *>(p.y)[size_t(tok) * p.M + row] = __float2half_rn(fmaf(sum, row_scale[j] * tokmul[tok], row_bias[j]));
             } else {
@@ -875,24 +893,76 @@ static size_t gemv_smem_bytes(int KP, int tokens, int nt) {
 
 static int token_tiles(int tokens) { return tokens <= 8 ? 1 : (tokens <= 16 ? 2 : 4); }
 
-// Largest number of tokens one pass can take for this K (shared-memory bound), capped at 32.
-static int tokens_per_pass(int KP) {
+constexpr int kMaxSplits = 16;
+static size_t split_smem_bytes(int KI, int splits, int tokens) {
+  return gemv_smem_bytes((KI + splits - 1) / splits * 128, tokens, token_tiles(tokens));
+}
+
+// K ranges for a pass that takes its activations from the pre-pass.  Every CTA keeps `tokens` rows of
+// its range in shared memory, so the ranges decide how many tokens fit and how many CTAs share an SM;
+// the price is splits * tokens * M fp32 sums written and read back.  Fewest ranges that (a) leave room
+// for two CTAs per SM, or failing that fit at all, and (b) give every SM two CTAs' worth of work items
+// while a range still holds eight units; 0 when `tokens` cannot be staged even with kMaxSplits ranges.
+static int choose_splits(const Handle *h, int tokens, int sm_count, size_t partial_floats) {
+  const int limit = std::min(kMaxSplits, h->KI);
+  int pick = 0;
+  for (int s = 1; s <= limit && !pick; ++s)
+    if (split_smem_bytes(h->KI, s, tokens) <= kSmemBudget / 2) pick = s;
+  for (int s = 1; s <= limit && !pick; ++s)
+    if (split_smem_bytes(h->KI, s, tokens) <= kSmemBudget) pick = s;
+  if (!pick) return 0;
+  while (pick < limit && h->MT * pick < 2 * sm_count && h->KI / (pick + 1) >= 8) ++pick;
+  while (pick > 1 && size_t(pick) * tokens * h->M > partial_floats) --pick;
+  return split_smem_bytes(h->KI, pick, tokens) <= kSmemBudget ? pick : 0;
+}
+
+// Largest number of tokens one pass can take (shared-memory bound with the most K ranges), capped at 32.
+static int tokens_per_pass(const Handle *h) {
   int best = 0;
   for (int tokens = 1; tokens <= 8 * kMaxTokenTiles; ++tokens)
-    if (gemv_smem_bytes(KP, tokens, token_tiles(tokens)) <= kSmemBudget) best = tokens;
+    if (split_smem_bytes(h->KI, std::min(kMaxSplits, h->KI), tokens) <= kSmemBudget) best = tokens;
   if (best >= 8) best = best / 8 * 8;   // whole token tiles when possible
   return best;
+}
+
+// y[t, m] = round(sum over the K ranges + bias): the second step of a pass with more than one range
+__global__ void __launch_bounds__(256) gemv_combine_kernel(const float *__restrict__ partial, int splits, const void *__restrict__ bias,
+                                                           void *__restrict__ y, int T, int M, int half_io) {
+  grid_dependency_wait();
+  const size_t total = size_t(T) * M;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    float sum = 0.f;
+    for (int s = 0; s < splits; ++s) sum += __ldcg(partial + size_t(s) * total + i);
+    const int row = int(i % M);
+    if (half_io) {
+      if (bias) sum += __half2float(static_cast<const __half *>(bias)[row]);
+      static_cast<__half *>(y)[i] = __float2half_rn(sum);
+    } else {
+      if (bias) sum += __bfloat162float(static_cast<const __nv_bfloat16 *>(bias)[row]);
+      static_cast<__nv_bfloat16 *>(y)[i] = __float2bfloat16(sum);
+    }
+  }
+}
+
+int launch_combine(const float *partial, int ranges, const void *bias, void *y, int tokens, int M, bool half_io, int sm_count,
+                   cudaStream_t stream) {
+  const int blocks = int(std::min<size_t>((size_t(tokens) * M + 255) / 256, size_t(sm_count) * 8));
+  TX_CUDA(launch_pdl(gemv_combine_kernel, dim3(blocks), dim3(256), 0, stream, partial, ranges, bias, y, tokens, M, half_io ? 1 : 0));
+  count_launch();
+  return TX_OK;
 }
 
 struct GemvPlan {
   GemvKernel kernel;
   SoloKernel solo_kernel;
   int nt, grid;
+  int splits;   // K ranges (pre-pass variants only)
   bool pre, solo;
   size_t smem;
 };
 
-static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, bool single_token_kernel = false, bool force_pre = false) {
+static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, bool single_token_kernel = false, bool force_pre = false,
+                     bool allow_splits = true) {
   Workspace *ws = workspace_for(h->device);
   if (!ws) return TX_ECUDA;
   int KP = h->KI * 128;
@@ -903,6 +973,11 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, 
   // The single-token kernel (no per-weight arithmetic) is taken on request only (tx_linear_single): it
   // pays off when its token arrives staged; staging a bf16 row costs it more than the general kernel.
   plan.solo = single_token_kernel;
+  plan.splits = 1;
+  if (plan.pre && !plan.solo && allow_splits) {
+    plan.splits = choose_splits(h, tokens, ws->sm_count, ws->partial_floats);
+    if (plan.splits < 1) return fail(TX_EINVAL, "decode GEMV does not fit in shared memory for this K");
+  }
   if (plan.solo) {
     plan.pre = false;
     plan.kernel = nullptr;
@@ -910,7 +985,7 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, 
     plan.smem = solo_smem_bytes(h->KI);
   } else {
     plan.kernel = pick_kernel(h->lookahead, plan.nt, plan.pre, needs_generic_variant(h), fuse);
-    plan.smem = gemv_smem_bytes(KP, tokens, plan.nt);
+    plan.smem = plan.pre ? split_smem_bytes(h->KI, plan.splits, tokens) : gemv_smem_bytes(KP, tokens, plan.nt);
   }
   // attribute + occupancy queries are cached per (device, kernel, shared bytes)
   static std::mutex guard;
@@ -931,7 +1006,8 @@ static int plan_gemv(const Handle *h, int tokens, GemvPlan &plan, int fuse = 0, 
   }
   if (per_sm < 1) return fail(TX_EINVAL, "decode GEMV does not fit in shared memory for this K");
   // persistent CTAs: one resident wave, each walking row tiles with stride gridDim.x
-  plan.grid = std::max(1, std::min(h->MT, ws->sm_count * std::min(per_sm, 3)));
+  const int slots = ws->sm_count * std::min(per_sm, 3);
+  plan.grid = std::max(1, std::min(h->MT, slots / plan.splits)) * plan.splits;   // a multiple of the K ranges
   return TX_OK;
 }
 
@@ -942,7 +1018,7 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
   Workspace *ws = workspace_for(h->device);
   if (!ws) return TX_ECUDA;
   int KP = h->KI * 128;
-  int per_pass = tokens_per_pass(KP);
+  int per_pass = tokens_per_pass(h);
   if (per_pass < 1) return fail(TX_EINVAL, "K is too large for the decode GEMV's shared-memory staging");
   for (int t0 = 0; t0 < tokens; t0 += per_pass) {
     int n = std::min(per_pass, tokens - t0);
@@ -971,9 +1047,15 @@ int launch_gemv(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int t
       count_launch();
       p.xprep = ws->xprep;
       p.xmul = ws->xmul;
+      p.splits = plan.splits;
+      p.partial = ws->partial;
     }
     TX_CUDA(launch_pdl(plan.kernel, dim3(plan.grid), dim3(kGemvThreads), plan.smem, stream, p));
     count_launch();
+    if (plan.pre && plan.splits > 1) {
+      rc = launch_combine(ws->partial, plan.splits, h->bias, p.y, n, h->M, half_io, ws->sm_count, stream);
+      if (rc != TX_OK) return rc;
+    }
   }
   TX_CUDA(cudaGetLastError());
   return TX_OK;
@@ -994,7 +1076,7 @@ int launch_gemv_fused(const Handle *h, const __nv_bfloat16 *x, const __nv_bfloat
       return other && a < b + bytes && b < a + mine;
     };
     if (overlaps(x, size_t(tokens) * h->K * 2)) return fail(TX_EINVAL, "residual_out must not alias x");
-    if (overlaps(delta, size_t(tokens) * h->K * 2) || overlaps(y, size_t(tokens) * h->M * 2))
+    if (overlaps(delta, size_t(tokens) * h->K * 2) || overlaps(y, size_t(tokens) * (swiglu ? h->M / 2 : h->M) * 2))
       return fail(TX_EINVAL, "residual_out must not overlap delta or y");
   }
   if (swiglu && h->M % 16) return fail(TX_EINVAL, "SwiGLU pairs need M to be a multiple of 16");
@@ -1179,6 +1261,7 @@ int launch_gemv_static_scratch(const Handle *h, const __nv_bfloat16 *x, __nv_bfl
   p.palette = h->palette;
   p.xprep = scratch->activations;
   p.xmul = scratch->multipliers;
+  p.splits = 1;   // whole rows per CTA: no partial-sum scratch
   gemv_xprep_kernel<false><<<tokens, kGemvThreads, 0, stream>>>(x, scratch->activations, scratch->multipliers, h->K, KP);
   count_launch();
   const int grid = std::max(1, std::min(h->MT, scratch->sm_count * std::min(per_sm, 3)));

@@ -84,6 +84,7 @@ struct PrefillParams {
   int M, K, KI, MT, T;
   int palette;
   int half_io;   // bias and y are fp16 (the staged activations are fp16 either way)
+  float *partial;   // gridDim.z > 1: K is cut into gridDim.z ranges of units and the scaled fp32 sums go to partial[range][T][M]
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -207,7 +208,9 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
   const unsigned a_s = tiles_s, b_s = tiles_s + S * Cfg::a_stage;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int KT = p.KI * kSubs;                           // pipeline stages over K
+  // this CTA's range of 128-column units (the whole row unless the launch cuts K)
+  const int u0 = int(blockIdx.z) * p.KI / int(gridDim.z), u1 = (int(blockIdx.z) + 1) * p.KI / int(gridDim.z);
+  const int KT = (u1 - u0) * kSubs;                      // pipeline stages over this range
   const int row0 = blockIdx.x * Cfg::rows, tok0 = blockIdx.y * BN;
 
   if (tid == 0) {
@@ -243,32 +246,43 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
       src[m] = p.tiles + (size_t(live[m] ? rt : 0) * p.KI) * 64 + half0 * 32 + lane;
       fl[m] = p.flags + size_t(live[m] ? rt : 0) * p.KI;
     }
-    uint4 q[MT][kHalvesPerWarp];
-    unsigned flag[MT];
+    // kLook units of every tile in flight per warp as register loads.  One is enough: four measured the same at
+    // 32 tokens (the pace there is set by the stage hand-over, not by DRAM latency) and 10 % slower at 512 tokens
+    constexpr int kLook = 1;
+    uint4 q[kLook][MT][kHalvesPerWarp];
+    unsigned flag[kLook][MT];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
+    for (int slot = 0; slot < kLook; ++slot)
 #pragma unroll
-      for (int h = 0; h < kHalvesPerWarp; ++h) q[m][h] = ldg_stream(src[m] + h * 32);
-      flag[m] = fl[m][0];
-    }
+      for (int m = 0; m < MT; ++m) {
+        if (u0 + slot < u1) {
+#pragma unroll
+          for (int h = 0; h < kHalvesPerWarp; ++h) q[slot][m][h] = ldg_stream(src[m] + size_t(u0 + slot) * 64 + h * 32);
+          flag[slot][m] = fl[m][u0 + slot];
+        }
+      }
     bool ok = true;
-    for (int unit = 0; unit < p.KI && ok; ++unit) {
+    for (int base = u0; base < u1 && ok; base += kLook) {
+#pragma unroll
+     for (int slot = 0; slot < kLook; ++slot) {
+      const int unit = base + slot;
+      if (unit >= u1 || !ok) break;                      // warp-uniform
       uint4 cq[MT][kHalvesPerWarp];
       unsigned cflag[MT];
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
-        cflag[m] = flag[m];
+        cflag[m] = flag[slot][m];
 #pragma unroll
-        for (int h = 0; h < kHalvesPerWarp; ++h) cq[m][h] = q[m][h];
-        if (unit + 1 < p.KI) {                           // next unit in flight while this one is decoded
+        for (int h = 0; h < kHalvesPerWarp; ++h) cq[m][h] = q[slot][m][h];
+        if (unit + kLook < u1) {                         // refill the slot
 #pragma unroll
-          for (int h = 0; h < kHalvesPerWarp; ++h) q[m][h] = ldg_stream(src[m] + size_t(unit + 1) * 64 + h * 32);
-          flag[m] = fl[m][unit + 1];
+          for (int h = 0; h < kHalvesPerWarp; ++h) q[slot][m][h] = ldg_stream(src[m] + size_t(unit + kLook) * 64 + h * 32);
+          flag[slot][m] = fl[m][unit + kLook];
         }
       }
 #pragma unroll
       for (int part = 0; part < kSubs; ++part) {
-        const int kt = unit * kSubs + part, s = kt % S;
+        const int kt = (unit - u0) * kSubs + part, s = kt % S;
         if (kt >= S && !mbar_wait(empty + 8 * s, ((kt / S) - 1) & 1, abort_flag, p.status, 1)) {
           ok = false;
           break;
@@ -302,6 +316,7 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
         __syncwarp();
         if (lane == 0) mbar_arrive(full_a + 8 * s);
       }
+     }
     }
   } else if (warp == kTmaWarp) {
     // ---------------- TMA: staged X tile [BN tokens x BK columns] per stage ----------------
@@ -311,7 +326,7 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
         const int s = kt % S;
         if (kt >= S && !mbar_wait(empty + 8 * s, ((kt / S) - 1) & 1, abort_flag, p.status, 2)) break;
         mbar_expect_tx(full_b + 8 * s, Cfg::b_stage);
-        tma_load_3d(b_s + s * Cfg::b_stage, &x_map, full_b + 8 * s, 0, tok0 / 32, kt * Cfg::chunks);
+        tma_load_3d(b_s + s * Cfg::b_stage, &x_map, full_b + 8 * s, 0, tok0 / 32, (u0 * kSubs + kt) * Cfg::chunks);
         issued = kt + 1;
       }
       if (*abort_flag) {
@@ -366,7 +381,9 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int tok = tok0 + c * 32 + j;
-            if (tok < p.T) {
+            if (tok < p.T && gridDim.z > 1) {
+              p.partial[(size_t(blockIdx.z) * p.T + tok) * p.M + row] = __uint_as_float(v[j]) * (row_scale * __ldg(p.xmul + tok));
+            } else if (tok < p.T) {
               const float value = fmaf(__uint_as_float(v[j]), row_scale * __ldg(p.xmul + tok), bias);
               if (p.half_io) reinterpret_cast<__half *>(p.y)[size_t(tok) * p.M + row] = __float2half_rn(value);
               else p.y[size_t(tok) * p.M + row] = __float2bfloat16(value);
@@ -424,6 +441,17 @@ bool prefill_tile_eligible(const Handle *h, int backend, int tokens) {
   return backend_shape(backend).mt != 0 && tokens >= 1 && h->K % 16 == 0 && encode_tiled_entry() != nullptr;
 }
 
+// Short prompts on matrices with few rows leave most SMs without a CTA (5120 rows = 40 CTAs of 128 rows): K is
+// then cut into ranges, one CTA per (row block, token block, range), fp32 sums combined by a second kernel.  The
+// number of ranges depends on the matrix and the token count only -- never on the tile -- so that all tiles keep
+// adding in the same order and stay bitwise identical to each other (the autotuner's admission rule).
+static int prefill_k_ranges(const Handle *h, int tokens, const Workspace *ws) {
+  const int blocks = ((h->M + 127) / 128) * ((tokens + 127) / 128);
+  int ranges = std::min(std::min(ws->sm_count / std::max(blocks, 1), 8), h->KI / 4);
+  while (ranges > 1 && size_t(ranges) * tokens * h->M > ws->partial_floats) --ranges;
+  return std::max(ranges, 1);
+}
+
 template <int MT, int BN, int BK>
 static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y, int tokens, cudaStream_t stream, bool half_io) {
   using Cfg = TileConfig<MT, BN, BK>;
@@ -475,9 +503,15 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
     p.T = n;
     p.palette = h->palette;
     p.half_io = half_io ? 1 : 0;
-    dim3 grid((h->M + Cfg::rows - 1) / Cfg::rows, (n + BN - 1) / BN);
+    p.partial = ws->partial;
+    const int ranges = prefill_k_ranges(h, n, ws);
+    dim3 grid((h->M + Cfg::rows - 1) / Cfg::rows, (n + BN - 1) / BN, ranges);
     prefill_umma_kernel<MT, BN, BK><<<grid, kPrefillThreads, Cfg::smem, stream>>>(p, map);
     count_launch();
+    if (ranges > 1) {
+      int rc = launch_combine(ws->partial, ranges, h->bias, y + size_t(t0) * h->M, n, h->M, half_io, ws->sm_count, stream);
+      if (rc != TX_OK) return rc;
+    }
   }
   TX_CUDA(cudaGetLastError());
   return TX_OK;

@@ -69,6 +69,8 @@ C_API = {
     "tx_aux_allreduce_add_rmsnorm": (_i32, [_vp, _vp, _vp, _vp, _i32, ctypes.c_float, _vp, _vp, _i32, _i32, _vp, _vp]),
     "tx_aux_attention_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp]),
     "tx_aux_silu_mul": (_i32, [_vp, _vp, _i32, _i32, _vp]),
+    "tx_aux_silu_mul_pairs": (_i32, [_vp, _vp, _i32, _i32, _vp]),
+    "tx_aux_attention_step_batch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, ctypes.c_float, _vp]),
     "tx_launch_count": (ctypes.c_int64, []),
     "tx_linear_single": (_i32, [_u64, _vp, _vp, _i32, _vp, _vp, _i32, ctypes.c_size_t, _vp]),
     "tx_linear_single_info": (_i32, [_u64, _vp]),
@@ -372,6 +374,25 @@ class _Extension:
                                                     k_cache.data_ptr(), v_cache.data_ptr(), scratch.data_ptr(), out.data_ptr(),
                                                     q_heads, kv_heads, head_dim, k_cache.shape[1], float(head_dim) ** -0.5,
                                                     self._stream(qkv)))
+
+    def attention_step_batch(self, qkv, cos, sin, positions, k_cache, v_cache, scratch, out, q_heads: int, kv_heads: int,
+                             head_dim: int) -> None:
+        """``attention_step`` for one token of each sequence of a batch in one launch: ``qkv [B, ...]``, ``positions``
+        int64 ``[B]``, caches ``[B, kv_heads, max_len, head_dim]``, ``out [B, q_heads * head_dim]``."""
+        sequences, max_len = k_cache.shape[0], k_cache.shape[2]
+        if qkv.shape[0] != sequences or positions.numel() != sequences or not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+            raise ValueError("attention_step_batch: one qkv row, one position and one contiguous cache per sequence")
+        if scratch.numel() < sequences * self.attention_step_scratch_floats(q_heads, max_len):
+            raise ValueError("attention_step scratch is too small for this batch and cache length")
+        self._check(self._lib.tx_aux_attention_step_batch(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(),
+                                                          k_cache.data_ptr(), v_cache.data_ptr(), scratch.data_ptr(), out.data_ptr(),
+                                                          sequences, q_heads, kv_heads, head_dim, max_len, float(head_dim) ** -0.5,
+                                                          self._stream(qkv)))
+
+    def silu_mul_pairs(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+        """``silu_mul`` for rows in ``interleave_gate_up`` order (gate and up rows in alternating groups of eight)."""
+        tokens, two_i = gate_up.shape
+        self._check(self._lib.tx_aux_silu_mul_pairs(gate_up.data_ptr(), out.data_ptr(), tokens, two_i // 2, self._stream(gate_up)))
 
     def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
         tokens, two_i = gate_up.shape
