@@ -653,6 +653,26 @@ def run_batched(args, config) -> None:
         raise SystemExit(f"a device-side bounded wait ran out (status {bad}): the measurement is invalid")
 
 
+def run_micro_exchange(args, config) -> None:
+    """`--micro-exchange` (under torch.distributed.run): only the tensor-parallel exchange timing of this model's
+    hidden size -- 1000 back-to-back exchanges in one CUDA graph, with and without the exchange -- one JSON line."""
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("start with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N --micro-exchange")
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    result = micro_exchange(config, torch.device("cuda", local), rank, world)
+    if rank == 0:
+        print(json.dumps({"metric": "tp_exchange_microseconds", "unit": "us", "higher_is_better": False, **result}), flush=True)
+    sys.stdout.flush()
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0 if result["kernel_status"] == 0 else 4)
+
+
 def run_micro(args) -> None:
     """Small single-kernel case for profilers: `--micro MxK[xT]` packs enough random BC4 matrices of that
     shape to exceed L2, runs the linear on each in turn (CUDA events) and prints one JSON line."""
@@ -726,6 +746,7 @@ def main() -> None:
                         help="--batch: B >= 16 through the multi-token decode kernel (gemv), the tensor-core tile kernel (tiles), "
                              "or whichever measures faster per projection (tuned)")
     parser.add_argument("--threshold", type=int, default=16, help="--micro: prefill threshold (token counts below it take the decode kernel)")
+    parser.add_argument("--micro-exchange", action="store_true", help="tensor parallel: time the exchange alone (1000 in one graph)")
     parser.add_argument("--micro", default=None, help="MxK[xT]: time one linear shape alone (profiling aid)")
     parser.add_argument("--backend", type=int, default=5, help="prefill backend id for --micro with T >= 16")
     parser.add_argument("--decode-path", type=int, default=0, help="--micro: 0 mma.sync ALU decode, 1 exact ALU, 2 texture")
@@ -741,6 +762,8 @@ def main() -> None:
         config = dataclasses.replace(config, layers=args.layers, name=f"{config.name}-{args.layers}layers")
     if args.impl == "reference":
         run_reference_arm(args, config)
+    elif args.micro_exchange:
+        run_micro_exchange(args, config)
     elif args.batch:
         if args.prompt == 2048:
             args.prompt = 512          # configuration 5's prompt length

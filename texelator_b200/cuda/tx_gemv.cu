@@ -88,6 +88,7 @@ template <bool HALF>
 __global__ void __launch_bounds__(kGemvThreads) gemv_xprep_kernel(const void *__restrict__ x, __half *__restrict__ xprep,
                                                                  float *__restrict__ xmul, int K, int KP) {
   __shared__ unsigned warp_max[kGemvWarps];
+  grid_launch_dependents();      // the main kernel's first weight loads may overlap this pass
   grid_dependency_wait();
   int tok = blockIdx.x;
   const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + size_t(tok) * K);
@@ -928,6 +929,7 @@ static int tokens_per_pass(const Handle *h) {
 // y[t, m] = round(sum over the K ranges + bias): the second step of a pass with more than one range
 __global__ void __launch_bounds__(256) gemv_combine_kernel(const float *__restrict__ partial, int splits, const void *__restrict__ bias,
                                                            void *__restrict__ y, int T, int M, int half_io) {
+  grid_launch_dependents();
   grid_dependency_wait();
   const size_t total = size_t(T) * M;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {

@@ -163,6 +163,7 @@ __global__ void __launch_bounds__(kStageThreads) stage_activations_kernel(const 
                                                                           float *__restrict__ xmul, int K, int KP, int tokens,
                                                                           int padded_tokens, int half_in) {
   __shared__ unsigned warp_max[32];
+  grid_launch_dependents();      // the tile kernel may set up (barriers, TMEM, first weight loads) while this one runs
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = K / 8, padded = KP / 8;
   const int first = blockIdx.x * 8;
@@ -182,10 +183,13 @@ __global__ void __launch_bounds__(kStageThreads) stage_activations_kernel(const 
   float mult, inverse;
   token_scaling(m, mult, inverse);
   if (half_in) inverse = 1.f;   // fp16 activations (x then points to fp16) are the operand as they are
-  if (threadIdx.x < 8 && tok < tokens) xmul[tok] = inverse * kNumeratorScale;
+  if (threadIdx.x < 8 && tok < tokens && blockIdx.y == 0) xmul[tok] = inverse * kNumeratorScale;
   uint4 *dst = reinterpret_cast<uint4 *>(out);
   const uint4 *src = reinterpret_cast<const uint4 *>(x + size_t(tok < tokens ? tok : 0) * K);
-  for (int chunk = threadIdx.x >> 3; chunk < padded; chunk += kStageThreads / 8)
+  // few tokens give few CTAs: blockIdx.y cuts the conversion (not the scan above) into column slices
+  const int per_slice = (padded + int(gridDim.y) - 1) / int(gridDim.y);
+  const int slice_end = min(padded, (int(blockIdx.y) + 1) * per_slice);
+  for (int chunk = int(blockIdx.y) * per_slice + (threadIdx.x >> 3); chunk < slice_end; chunk += kStageThreads / 8)
     dst[size_t(chunk) * padded_tokens + tok] =
         (tok < tokens && chunk < chunks) ? (half_in ? src[chunk] : convert_chunk(src[chunk], mult)) : make_uint4(0, 0, 0, 0);
 }
@@ -208,6 +212,10 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
   const unsigned a_s = tiles_s, b_s = tiles_s + S * Cfg::a_stage;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // Launched with programmatic stream serialisation behind the staging kernel: everything up to the first read
+  // of the staged activations (the TMA lane) or of the token multipliers (the epilogue) touches only the
+  // immutable payload and this CTA's own memory and may run while the staging kernel is still at work.
+  grid_launch_dependents();
   // this CTA's range of 128-column units (the whole row unless the launch cuts K)
   const int u0 = int(blockIdx.z) * p.KI / int(gridDim.z), u1 = (int(blockIdx.z) + 1) * p.KI / int(gridDim.z);
   const int KT = (u1 - u0) * kSubs;                      // pipeline stages over this range
@@ -321,6 +329,7 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
   } else if (warp == kTmaWarp) {
     // ---------------- TMA: staged X tile [BN tokens x BK columns] per stage ----------------
     if (lane == 0) {
+      grid_dependency_wait();              // the staged activations are complete
       int issued = 0;
       for (int kt = 0; kt < KT; ++kt) {
         const int s = kt % S;
@@ -363,6 +372,7 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
 
   // ---------------- epilogue: TMEM -> registers -> y ----------------
   if (warp < kProducerWarps) {
+    grid_dependency_wait();                // xmul comes from the staging kernel
     const bool ready = mbar_wait(accum, 0, abort_flag, p.status, 5);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ready) {
@@ -474,7 +484,8 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
   for (int t0 = 0; t0 < tokens; t0 += capacity) {
     const int n = std::min(capacity, tokens - t0);
     const int padded_tokens = (n + 31) & ~31;
-    stage_activations_kernel<<<padded_tokens / 8, kStageThreads, 0, stream>>>(x + size_t(t0) * h->K, ws->xprep, ws->xmul, h->K, KP, n,
+    const int slices = std::max(1, std::min(16, ws->sm_count / (padded_tokens / 8)));
+    stage_activations_kernel<<<dim3(padded_tokens / 8, slices), kStageThreads, 0, stream>>>(x + size_t(t0) * h->K, ws->xprep, ws->xmul, h->K, KP, n,
                                                                     padded_tokens, half_io ? 1 : 0);
     count_launch();
     // staged X viewed as [KP/8 chunks][padded_tokens/32][32 tokens x 8 elements]: a box is BN/32 runs of
@@ -506,7 +517,7 @@ static int launch_tile(const Handle *h, const __nv_bfloat16 *x, __nv_bfloat16 *y
     p.partial = ws->partial;
     const int ranges = prefill_k_ranges(h, n, ws);
     dim3 grid((h->M + Cfg::rows - 1) / Cfg::rows, (n + BN - 1) / BN, ranges);
-    prefill_umma_kernel<MT, BN, BK><<<grid, kPrefillThreads, Cfg::smem, stream>>>(p, map);
+    TX_CUDA(launch_pdl(prefill_umma_kernel<MT, BN, BK>, grid, dim3(kPrefillThreads), Cfg::smem, stream, p, map));
     count_launch();
     if (ranges > 1) {
       int rc = launch_combine(ws->partial, ranges, h->bias, y + size_t(t0) * h->M, n, h->M, half_io, ws->sm_count, stream);
