@@ -43,9 +43,14 @@ namespace tx {
 
 constexpr int kMmaM = 128;               // rows of one tcgen05.mma (TMEM lanes)
 constexpr int kASbo = 128;               // byte stride between 8-row groups of the A tile
+// Sixteen producer warps, one 8-row half of a 16-row tile each, all on every pipeline stage.  Measured and not
+// adopted: two groups of eight warps taking alternate stages with a whole tile per warp (same speed at 32 and
+// 128 tokens, 2-4 % slower at 512), a four-unit register look-ahead (same / 10 % slower), a 128 x 32 tile with a
+// five-stage ring against the 128 x 64 tile with four stages at 32 tokens (same).
 constexpr int kProducerWarps = 16;              // 8: one 16-row tile per warp; 16: one 8-row half of a tile per warp
 constexpr int kTileWarps = 8;                   // 16-row tiles of one 128-row accumulator
-constexpr int kHalvesPerWarp = 16 / kProducerWarps;
+constexpr int kGroups = 1;                      // groups of producer warps that take alternate units
+constexpr int kHalvesPerWarp = 16 * kGroups / kProducerWarps;
 constexpr int kTmaWarp = kProducerWarps, kMmaWarp = kProducerWarps + 1;
 constexpr int kPrefillThreads = (kProducerWarps + 2) * 32;   // producer/epilogue warps + TMA warp + MMA warp
 static_assert(kProducerWarps == 8 || kProducerWarps == 16, "producer warps split tiles whole or by halves");
@@ -223,7 +228,7 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full_a + 8 * s, kProducerWarps);
+      mbar_init(full_a + 8 * s, kProducerWarps / kGroups);
       mbar_init(full_b + 8 * s, 1);
       mbar_init(empty + 8 * s, 1);
     }
@@ -243,7 +248,8 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
   if (warp < kProducerWarps) {
     // ---------------- producers: BC4 -> fp16 A tile; warp w owns 16-row tiles w, w+8, ... of the CTA ----------------
     const int g = lane >> 2, t = lane & 3;
-    const int tile_warp = warp % kTileWarps, half0 = warp / kTileWarps;   // half0 is 0 with eight producers
+    const int tile_warp = warp % kTileWarps;
+    const int group = kGroups > 1 ? warp / kTileWarps : 0, half0 = kGroups > 1 ? 0 : warp / kTileWarps;   // half0 is 0 with eight producers
     const uint4 *src[MT];
     const uint8_t *fl[MT];
     bool live[MT];
@@ -263,17 +269,17 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
     for (int slot = 0; slot < kLook; ++slot)
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
-        if (u0 + slot < u1) {
+        if (u0 + group + slot * kGroups < u1) {
 #pragma unroll
-          for (int h = 0; h < kHalvesPerWarp; ++h) q[slot][m][h] = ldg_stream(src[m] + size_t(u0 + slot) * 64 + h * 32);
-          flag[slot][m] = fl[m][u0 + slot];
+          for (int h = 0; h < kHalvesPerWarp; ++h) q[slot][m][h] = ldg_stream(src[m] + size_t(u0 + group + slot * kGroups) * 64 + h * 32);
+          flag[slot][m] = fl[m][u0 + group + slot * kGroups];
         }
       }
     bool ok = true;
-    for (int base = u0; base < u1 && ok; base += kLook) {
+    for (int base = u0 + group; base < u1 && ok; base += kLook * kGroups) {
 #pragma unroll
      for (int slot = 0; slot < kLook; ++slot) {
-      const int unit = base + slot;
+      const int unit = base + slot * kGroups;
       if (unit >= u1 || !ok) break;                      // warp-uniform
       uint4 cq[MT][kHalvesPerWarp];
       unsigned cflag[MT];
@@ -282,10 +288,10 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
         cflag[m] = flag[slot][m];
 #pragma unroll
         for (int h = 0; h < kHalvesPerWarp; ++h) cq[m][h] = q[slot][m][h];
-        if (unit + kLook < u1) {                         // refill the slot
+        if (unit + kLook * kGroups < u1) {               // refill the slot with this warp's next unit
 #pragma unroll
-          for (int h = 0; h < kHalvesPerWarp; ++h) q[slot][m][h] = ldg_stream(src[m] + size_t(unit + kLook) * 64 + h * 32);
-          flag[slot][m] = fl[m][unit + kLook];
+          for (int h = 0; h < kHalvesPerWarp; ++h) q[slot][m][h] = ldg_stream(src[m] + size_t(unit + kLook * kGroups) * 64 + h * 32);
+          flag[slot][m] = fl[m][unit + kLook * kGroups];
         }
       }
 #pragma unroll
@@ -315,8 +321,9 @@ prefill_umma_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap x
               // block kb of the stage -> K chunks 2kb, 2kb+1; row = (m*8 + tile_warp)*16 + half*8 + g
               const int kb = (kSubs == 2 ? 0 : sub * 4) + t;
               uint8_t *dst = stage + (2 * kb) * Cfg::a_lbo + ((m * kTileWarps + tile_warp) * 2 + half) * kASbo + g * 16;
-              *reinterpret_cast<uint4 *>(dst) = live[m] ? make_uint4(packed[0], packed[1], packed[2], packed[3]) : make_uint4(0, 0, 0, 0);
-              *reinterpret_cast<uint4 *>(dst + Cfg::a_lbo) = live[m] ? make_uint4(packed[4], packed[5], packed[6], packed[7]) : make_uint4(0, 0, 0, 0);
+              // (row tiles past the end of the matrix decode tile 0 again: their accumulator rows are never stored)
+              *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              *reinterpret_cast<uint4 *>(dst + Cfg::a_lbo) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
             }
           }
         }
