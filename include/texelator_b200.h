@@ -201,8 +201,10 @@ int tx_kernel_status(int device, int clear);
  *                      caches [kv_heads, max_len, head_dim] at *position (device int64)
  *   attention_decode : one query per head over cache positions 0..*position, grouped-query; `scratch`
  *                      holds q_heads * ceil(max_len/128) * (head_dim+2) floats; head_dim must be 128
- *   attention_step   : rope_append + attention_decode of one token in ONE launch (q is rotated on the
- *                      fly, qkv is left untouched); `scratch` holds q_heads * ceil(max_len/64) * 132
+ *   attention_step   : rope_append + attention_decode of one token in one call (q is rotated on the
+ *                      fly, qkv is left untouched): one launch over 64-key splits of the cache and a small
+ *                      dependent launch that merges them (TEXELATOR_B200_ATTENTION_MERGE=inline: one launch,
+ *                      the last split's CTA merges); `scratch` holds q_heads * ceil(max_len/64) * 132
  *                      floats; head_dim 128; long caches are walked in 64-key chunks per CTA
  *   silu_mul         : out[t,i] = silu(gate_up[t,i]) * gate_up[t,intermediate+i]                     */
 int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, int tokens, int hidden, float eps, void *stream);

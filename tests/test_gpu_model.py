@@ -80,14 +80,14 @@ def test_fused_decode_step_matches_pytorch_glue():
         model.prefer_single = lambda: True                                   # the same path under graph replay
         model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
         model.capture()
-        assert model.launches_per_step == model.config.layers * 7 + 1
+        assert model.launches_per_step == model.config.layers * 8 + 1
         for step in range(3):
             model.decode_graph()
             torch.cuda.synchronize()
             assert _cosine(model.last_hidden, hidden[step]) >= 0.9995, step
         del model.prefer_single
         model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
-        for fuse_norm, per_layer in ((False, 7), (True, 5)):
+        for fuse_norm, per_layer in ((False, 8), (True, 6)):
             model.fuse_norm = fuse_norm
             model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
             model.capture()

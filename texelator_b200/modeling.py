@@ -402,7 +402,7 @@ class BC4Decoder:
         return self.peers is not None
 
     def _decode_step_single(self):
-        """One decode step on the single-token path, seven launches per layer.  The norm kernels write their
+        """One decode step on the single-token path, eight launches per layer (the attention step is two: splits, merge).  The norm kernels write their
         output in the staged form of ``tx_linear_single`` (the qkv and gate/up linears then copy 11 KB instead
         of each CTA scanning and converting the row).  On one GPU the o and down linears, whose inputs come
         from many CTAs, stage for themselves in the general decode kernel (``self.k_split`` lets them leave
@@ -448,7 +448,7 @@ class BC4Decoder:
         self.pos.add_(1)
 
     def _decode_step_fused(self):
-        """One decode step with the library's fused kernels, five launches per layer: qkv linear (with the
+        """One decode step with the library's fused kernels, six launches per layer with ``fuse_norm`` (eight without): qkv linear (with the
         residual add and RMSNorm in its activation staging), attention step (RoPE, cache append, attention,
         split merge), o linear, gate/up linear (add + norm in front, SwiGLU behind), down linear."""
         c, ext = self.config, self.ext
