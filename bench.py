@@ -503,6 +503,7 @@ def run_gpu_arm(args, config) -> None:
     model.prefill(ids)
     model.tok.fill_(int(ids[-1]))
     fused_allreduce = world > 1 and not args.nccl_allreduce and model.enable_peer_exchange()
+    model.fuse_norm = bool(args.fuse_norm)
     model.capture()
     steps, warmup = args.steps, max(args.warmup, 3)
 
@@ -746,6 +747,7 @@ def main() -> None:
                         help="--batch: B >= 16 through the multi-token decode kernel (gemv), the tensor-core tile kernel (tiles), "
                              "or whichever measures faster per projection (tuned)")
     parser.add_argument("--threshold", type=int, default=16, help="--micro: prefill threshold (token counts below it take the decode kernel)")
+    parser.add_argument("--fuse-norm", action="store_true", help="residual add + RMSNorm inside the qkv and gate/up linears (A/B aid; default: separate norm kernels)")
     parser.add_argument("--micro-exchange", action="store_true", help="tensor parallel: time the exchange alone (1000 in one graph)")
     parser.add_argument("--micro", default=None, help="MxK[xT]: time one linear shape alone (profiling aid)")
     parser.add_argument("--backend", type=int, default=5, help="prefill backend id for --micro with T >= 16")
