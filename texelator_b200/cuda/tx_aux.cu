@@ -1245,17 +1245,22 @@ __global__ void __launch_bounds__(256) silu_mul_pairs_kernel(const __nv_bfloat16
 // dimension d.  As a programmatic dependent of the step kernel it is resident and waiting when the last split
 // finishes, which costs less than the fence -> atomic -> last-CTA chain inside the step kernel (the kernel
 // boundary orders the partial records; no arrival counter is needed).
-__global__ void __launch_bounds__(kHeadDim) attention_merge_kernel(const float *__restrict__ partial, const long long *__restrict__ position,
-                                                                  __nv_bfloat16 *__restrict__ out, int q_heads, int split_capacity,
-                                                                  int live_cap) {
+constexpr int kMergeParts = 4;      // thread groups of one CTA that share a head's splits
+__global__ void __launch_bounds__(kHeadDim * kMergeParts) attention_merge_kernel(const float *__restrict__ partial,
+                                                                                const long long *__restrict__ position,
+                                                                                __nv_bfloat16 *__restrict__ out, int q_heads,
+                                                                                int split_capacity, int live_cap) {
   __shared__ float weight_s[kStepMaxSplits];
+  __shared__ float sum_s[kMergeParts][kHeadDim];
   __shared__ float inverse_s;
   const int head = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int d = tid % kHeadDim, part = tid / kHeadDim;      // output dimension, share of the splits
   grid_launch_dependents();
   grid_dependency_wait();
   const long long pos = __ldcg(position + seq);
   const int live = min(int(pos / kStepKeys) + 1, live_cap);
   const float *base = partial + (size_t(seq) * q_heads + head) * split_capacity * kStepRow;
+  // warp 0 turns the (max, sum) records into weights while every group already has its first records in flight
   if (warp == 0) {
     constexpr int kPerLane = kStepMaxSplits / 32;
     float2 rec[kPerLane];
@@ -1279,16 +1284,44 @@ __global__ void __launch_bounds__(kHeadDim) attention_merge_kernel(const float *
     den = warp_sum(den);
     if (lane == 0) inverse_s = 1.f / den;
   }
-  __syncthreads();
-  float even = 0.f, odd = 0.f;                     // two chains; the loads are independent of them
-  int sp = 0;
-#pragma unroll 4
-  for (; sp + 1 < live; sp += 2) {
-    even = fmaf(weight_s[sp], __ldcg(base + size_t(sp) * kStepRow + tid), even);
-    odd = fmaf(weight_s[sp + 1], __ldcg(base + size_t(sp + 1) * kStepRow + tid), odd);
+  // this group's records: split part, part + kMergeParts, ... in rounds of eight loads; the first round is issued
+  // before the barrier that publishes the weights
+  constexpr int kRounds = kStepMaxSplits / kMergeParts / 8;
+  float value[8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int sp = part + i * kMergeParts;
+    value[i] = sp < live ? __ldcg(base + size_t(sp) * kStepRow + d) : 0.f;
   }
-  if (sp < live) even = fmaf(weight_s[sp], __ldcg(base + size_t(sp) * kStepRow + tid), even);
-  out[(size_t(seq) * q_heads + head) * kHeadDim + tid] = __float2bfloat16((even + odd) * inverse_s);
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int sp = part + i * kMergeParts;
+    if (sp < live) sum = fmaf(weight_s[sp], value[i], sum);
+  }
+  for (int round = 1; round < kRounds; ++round) {
+    const int first = round * 8 * kMergeParts + part;
+    if (first >= live) break;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int sp = first + i * kMergeParts;
+      value[i] = sp < live ? __ldcg(base + size_t(sp) * kStepRow + d) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int sp = first + i * kMergeParts;
+      if (sp < live) sum = fmaf(weight_s[sp], value[i], sum);
+    }
+  }
+  sum_s[part][d] = sum;
+  __syncthreads();
+  if (part == 0) {
+    float total = sum_s[0][d];
+#pragma unroll
+    for (int p = 1; p < kMergeParts; ++p) total += sum_s[p][d];
+    out[(size_t(seq) * q_heads + head) * kHeadDim + d] = __float2bfloat16(total * inverse_s);
+  }
 }
 
 // TEXELATOR_B200_ATTENTION_MERGE=inline keeps the merge inside the step kernel (one launch per step instead of
@@ -1315,7 +1348,7 @@ static cudaError_t launch_attention_step(int splits, int kv_heads, int sequences
                         position, k_cache, v_cache, scratch, out, q_heads, kv_heads, max_len, splits, scale, merge_here);
   if (status != cudaSuccess || merge_here) return status;
   count_launch();
-  return launch_pdl(attention_merge_kernel, dim3(q_heads, sequences), dim3(kHeadDim), 0, s, static_cast<const float *>(scratch), position, out,
+  return launch_pdl(attention_merge_kernel, dim3(q_heads, sequences), dim3(kHeadDim * kMergeParts), 0, s, static_cast<const float *>(scratch), position, out,
                     q_heads, splits, LOOP ? splits : kStepMaxSplits);
 }
 
