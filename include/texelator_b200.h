@@ -205,7 +205,10 @@ int tx_kernel_status(int device, int clear);
  *                      fly, qkv is left untouched): one launch over 64-key splits of the cache and a small
  *                      dependent launch that merges them (TEXELATOR_B200_ATTENTION_MERGE=inline: one launch,
  *                      the last split's CTA merges); `scratch` holds q_heads * ceil(max_len/64) * 132
- *                      floats; head_dim 128; long caches are walked in 64-key chunks per CTA
+ *                      floats; head_dim 128; long caches are walked in 64-key chunks per CTA.  `position` and
+ *                      the cache rows below it are read before the kernel waits for the launch in front of it
+ *                      (they overlap that launch's tail): they must be complete when that launch starts, as they
+ *                      are in a decode loop, where earlier steps wrote them
  *   silu_mul         : out[t,i] = silu(gate_up[t,i]) * gate_up[t,intermediate+i]                     */
 int tx_aux_add_rmsnorm(void *h, const void *delta, const void *weight, void *y, int tokens, int hidden, float eps, void *stream);
 /* add_rmsnorm for one token with the extras of tx_linear_single: delta may come as `splits` fp32 partial

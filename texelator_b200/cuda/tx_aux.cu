@@ -741,13 +741,37 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_kernel(const _
   out += size_t(blockIdx.z) * q_heads * kHeadDim;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   grid_launch_dependents();
-  grid_dependency_wait();
+  // The position and the cache rows below it were written by earlier steps (no launch of this library writes
+  // them, and a foreign kernel directly in front would have to finish first), so they are read before the wait
+  // for the launch in front -- the qkv linear, whose tail these loads overlap.  Only qkv itself is new.
   const long long pos = __ldcg(position);                       // attends to keys 0..pos; key pos is new
   const int live = int(pos / kStepKeys) + 1;                    // splits that hold at least one key
   if (split >= live) return;
   const int key0 = split * kStepKeys;
   const int count = int(min((long long)kStepKeys, pos + 1 - key0));
   const size_t q_rows = size_t(q_heads) * kHeadDim, kv_rows = size_t(kv_heads) * kHeadDim;
+
+  // ---- all old cache rows of this CTA in flight at once ----
+  // keys: lane (r = lane >> 3, j = lane & 7) holds dimensions 8j..8j+7 and 64+8j..64+8j+7 of key
+  // warp*8 + batch*4 + r; values: lane holds dimensions 4*lane..4*lane+3 of key warp*8 + i
+  const int r = lane >> 3, j = lane & 7;
+  uint4 key_raw[2][2];
+  uint2 val_raw[8];
+#pragma unroll
+  for (int b = 0; b < 2; ++b) {
+    const int key = warp * 8 + b * 4 + r;
+    const uint4 *row = reinterpret_cast<const uint4 *>(k_cache + (size_t(kvh) * max_len + key0 + key) * kHeadDim);
+    const bool old_row = key0 + key < pos;
+    key_raw[b][0] = old_row ? __ldcg(row + j) : make_uint4(0, 0, 0, 0);
+    key_raw[b][1] = old_row ? __ldcg(row + 8 + j) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int key = warp * 8 + i;
+    val_raw[i] = key0 + key < pos ? __ldcg(reinterpret_cast<const uint2 *>(v_cache + (size_t(kvh) * max_len + key0 + key) * kHeadDim) + lane)
+                                  : make_uint2(0, 0);
+  }
+  grid_dependency_wait();
 
   // ---- prologue: rotate-half RoPE of q (and of the new key by its owner) ----
   for (int idx = tid; idx < GROUP * kHalf; idx += kStepThreads) {
@@ -775,25 +799,20 @@ __global__ void __launch_bounds__(kStepThreads, 2) attention_step_kernel(const _
   }
   __syncthreads();
 
-  // ---- all cache rows of this CTA in flight at once ----
-  // keys: lane (r = lane >> 3, j = lane & 7) holds dimensions 8j..8j+7 and 64+8j..64+8j+7 of key
-  // warp*8 + batch*4 + r; values: lane holds dimensions 4*lane..4*lane+3 of key warp*8 + i
-  const int r = lane >> 3, j = lane & 7;
-  uint4 key_raw[2][2];
-  uint2 val_raw[8];
+  // ---- the new row (written above by this CTA when it owns the last split) ----
 #pragma unroll
   for (int b = 0; b < 2; ++b) {
     const int key = warp * 8 + b * 4 + r;
-    const uint4 *row = reinterpret_cast<const uint4 *>(k_cache + (size_t(kvh) * max_len + key0 + key) * kHeadDim);
-    key_raw[b][0] = key < count ? __ldcg(row + j) : make_uint4(0, 0, 0, 0);
-    key_raw[b][1] = key < count ? __ldcg(row + 8 + j) : make_uint4(0, 0, 0, 0);
+    if (key0 + key == pos) {
+      const uint4 *row = reinterpret_cast<const uint4 *>(k_cache + (size_t(kvh) * max_len + pos) * kHeadDim);
+      key_raw[b][0] = __ldcg(row + j);
+      key_raw[b][1] = __ldcg(row + 8 + j);
+    }
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int key = warp * 8 + i;
-    val_raw[i] = key < count ? __ldcg(reinterpret_cast<const uint2 *>(v_cache + (size_t(kvh) * max_len + key0 + key) * kHeadDim) + lane)
-                             : make_uint2(0, 0);
-  }
+  for (int i = 0; i < 8; ++i)
+    if (key0 + warp * 8 + i == pos)
+      val_raw[i] = __ldcg(reinterpret_cast<const uint2 *>(v_cache + (size_t(kvh) * max_len + pos) * kHeadDim) + lane);
 
   // ---- scores (q of one head at a time, so that two CTAs fit the register file of an SM) ----
   {
