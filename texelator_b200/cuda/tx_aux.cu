@@ -31,8 +31,16 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16
                                                                    int hidden, float eps) {
   __shared__ float partial[kNormThreads / 32];
   grid_launch_dependents();
-  grid_dependency_wait();
   const int row = blockIdx.x, chunks = hidden / 8;
+  // the norm weight is immutable: fetch it while the launch in front is still running
+  const uint4 *wr = reinterpret_cast<const uint4 *>(weight);
+  uint4 gain[kNormChunks];
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    if (i < chunks) gain[c] = wr[i];
+  }
+  grid_dependency_wait();
   uint4 *hr = reinterpret_cast<uint4 *>(h + size_t(row) * hidden);
   const uint4 *dr = delta ? reinterpret_cast<const uint4 *>(delta + size_t(row) * hidden) : nullptr;
   uint4 keep[kNormChunks];
@@ -68,13 +76,12 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__nv_bfloat16
 #pragma unroll
   for (int w = 0; w < kNormThreads / 32; ++w) total += partial[w];
   const float inv = rsqrtf(total / float(hidden) + eps);
-  const uint4 *wr = reinterpret_cast<const uint4 *>(weight);
   uint4 *yr = reinterpret_cast<uint4 *>(y + size_t(row) * hidden);
 #pragma unroll
   for (int c = 0; c < kNormChunks; ++c) {
     const int i = threadIdx.x + c * kNormThreads;
     if (i < chunks) {
-      uint4 v = keep[c], w = wr[i], o;
+      uint4 v = keep[c], w = gain[c], o;
       const __nv_bfloat162 *pv = reinterpret_cast<const __nv_bfloat162 *>(&v), *pw = reinterpret_cast<const __nv_bfloat162 *>(&w);
       __nv_bfloat162 *po = reinterpret_cast<__nv_bfloat162 *>(&o);
 #pragma unroll
@@ -108,8 +115,16 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_single_kernel(__nv_b
   __shared__ float partial[kNormThreads / 32];
   __shared__ unsigned peak[kNormThreads / 32];
   grid_launch_dependents();
-  grid_dependency_wait();
   const int chunks = hidden / 8, lane = threadIdx.x & 31;
+  // the norm weight is immutable: fetch it while the launch in front is still running
+  const uint4 *wr = reinterpret_cast<const uint4 *>(weight);
+  uint4 gain[kNormChunks];
+#pragma unroll
+  for (int c = 0; c < kNormChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    if (i < chunks) gain[c] = wr[i];
+  }
+  grid_dependency_wait();
   uint4 *hr = reinterpret_cast<uint4 *>(h);
   const uint4 *dr = delta ? reinterpret_cast<const uint4 *>(delta) : nullptr;
   uint4 keep[kNormChunks];
@@ -160,14 +175,13 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_single_kernel(__nv_b
 #pragma unroll
   for (int w = 0; w < kNormThreads / 32; ++w) total += partial[w];
   const float inv = rsqrtf(total / float(hidden) + eps);
-  const uint4 *wr = reinterpret_cast<const uint4 *>(weight);
   uint4 *yr = reinterpret_cast<uint4 *>(y);
   unsigned m = 0;
 #pragma unroll
   for (int c = 0; c < kNormChunks; ++c) {
     const int i = threadIdx.x + c * kNormThreads;
     if (i < chunks) {
-      uint4 v = keep[c], w = wr[i], o;
+      uint4 v = keep[c], w = gain[c], o;
       const __nv_bfloat162 *pv = reinterpret_cast<const __nv_bfloat162 *>(&v), *pw = reinterpret_cast<const __nv_bfloat162 *>(&w);
       __nv_bfloat162 *po = reinterpret_cast<__nv_bfloat162 *>(&o);
 #pragma unroll
@@ -349,11 +363,13 @@ __global__ void __launch_bounds__(kReduceThreads) peer_reduce_rmsnorm_kernel(con
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int ctas = int(cluster.num_blocks()), cta = int(cluster.block_rank());
   grid_launch_dependents();
-  grid_dependency_wait();
   const int chunks = p.hidden / 8;
   const int per = (((chunks + ctas - 1) / ctas) + 1) & ~1;            // even: the two chunks of a block stay in one warp
   const int i = cta * per + tid;
   const bool live = tid < per && i < chunks;
+  // the norm weight is immutable: fetch it while the launch in front is still running
+  const uint4 gain = live ? reinterpret_cast<const uint4 *>(p.weight)[i] : make_uint4(0, 0, 0, 0);
+  grid_dependency_wait();
   const unsigned epoch = p.world ? __ldcg(p.epoch_word) + 1u : 0u;
 
   uint4 v = make_uint4(0, 0, 0, 0);
@@ -430,7 +446,7 @@ __global__ void __launch_bounds__(kReduceThreads) peer_reduce_rmsnorm_kernel(con
   uint4 o = make_uint4(0, 0, 0, 0);
   unsigned m = 0;
   if (live) {
-    const uint4 w = reinterpret_cast<const uint4 *>(p.weight)[i];
+    const uint4 w = gain;
     const __nv_bfloat162 *pv = reinterpret_cast<const __nv_bfloat162 *>(&v), *pw = reinterpret_cast<const __nv_bfloat162 *>(&w);
     __nv_bfloat162 *po = reinterpret_cast<__nv_bfloat162 *>(&o);
 #pragma unroll
