@@ -156,7 +156,7 @@ class BC4Decoder:
     """
 
     def __init__(self, config: DecoderConfig, device, max_len: int, seed: int = 0, tp_rank: int = 0,
-                 tp_world: int = 1, group=None, lookahead: int = 4, keep_dense: bool = False,
+                 tp_world: int = 1, group=None, lookahead: int = 3, keep_dense: bool = False,
                  weight_std: float = 0.02, prefill_backend: int = 5):
         self.config, self.device, self.max_len = config, torch.device(device), max_len
         self.rank, self.world, self.group = tp_rank, tp_world, group
