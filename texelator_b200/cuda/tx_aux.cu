@@ -1291,10 +1291,10 @@ __global__ void __launch_bounds__(kHeadDim * kMergeParts) attention_merge_kernel
   const int head = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int d = tid % kHeadDim, part = tid / kHeadDim;      // output dimension, share of the splits
   grid_launch_dependents();
-  grid_dependency_wait();
-  const long long pos = __ldcg(position + seq);
+  const long long pos = __ldcg(position + seq);     // written by an earlier step: safe to read before the wait
   const int live = min(int(pos / kStepKeys) + 1, live_cap);
   const float *base = partial + (size_t(seq) * q_heads + head) * split_capacity * kStepRow;
+  grid_dependency_wait();
   // warp 0 turns the (max, sum) records into weights while every group already has its first records in flight
   if (warp == 0) {
     constexpr int kPerLane = kStepMaxSplits / 32;
