@@ -21,11 +21,21 @@ def ext():
 
 
 def _encode(m, k, seed):
-    from texelator_b200.modeling import encode_minmax_cuda, software_palette_table
+    """A full-size matrix through the reference's E3 encoder (the GPU implementation, byte-identical to the
+    reference's recorded output in test_gpu_encode.py; 64 rows are re-checked here against the CPU restatement)."""
+    from texelator_b200 import runtime
+    from texelator_b200.modeling import software_palette_table
     gen = torch.Generator(device="cuda").manual_seed(seed)
     weight = torch.randn(m, k, device="cuda", generator=gen) * 0.02
     weight[torch.rand(m, k, device="cuda", generator=gen) < 0.002] = 0       # a few low-mode blocks now and then
-    blocks, scales = encode_minmax_cuda(weight, software_palette_table("cuda"))
+    calibration = torch.randn(64, k, device="cuda", generator=gen)
+    hdiag = (calibration * calibration).mean(0)
+    table = software_palette_table("cuda")
+    blocks, scales = runtime.extension().encode(weight, hdiag, table)
+    rows = np.random.default_rng(seed).choice(m, 64, replace=False)
+    want_blocks, want_scales = O.encode_linear(weight[rows].cpu(), hdiag.cpu(), table.cpu().numpy())
+    assert np.array_equal(blocks.cpu().numpy().reshape(m, k // 2)[rows].reshape(-1), want_blocks)
+    assert np.array_equal(scales.cpu().numpy()[rows], want_scales)
     x = torch.randn(1, k, device="cuda", generator=gen).bfloat16()
     return blocks, scales, x
 
@@ -115,17 +125,16 @@ CFG3_SHAPES = [(5120, 5120), (17408, 5120), (5120, 17408)]          # (M, K)
 def test_prefill_sweep_points_match_oracle(ext, lut, m, k, tokens):
     """Every point of the prefill sweep through the tile the autotuner would pick for it (all candidates are
     bitwise identical, checked here on the fly), against the dequantise-then-matmul oracle on 96 sampled
-    output rows.  The first 512 rows of the matrix carry weights encoded by the restated reference encoder
-    (activation-weighted endpoint search), the rest the min/max fill."""
-    from texelator_b200.modeling import encode_minmax_cuda, software_palette_table
+    output rows.  The whole matrix is encoded by the reference's activation-weighted endpoint search (GPU
+    encoder); the first 512 rows are encoded a second time by the CPU restatement and must come out the same."""
     gen = torch.Generator(device="cuda").manual_seed(3 * m + k + tokens)
     weight = torch.randn(m, k, device="cuda", generator=gen) * 0.02
-    blocks, scales = encode_minmax_cuda(weight, software_palette_table("cuda"))
     calibration = torch.randn(64, k, generator=torch.Generator().manual_seed(k))
-    real_blocks, real_scales = O.encode_linear(weight[:512].cpu(), (calibration * calibration).mean(0), lut)
-    blocks = blocks.clone()
-    blocks[:real_blocks.size] = torch.from_numpy(real_blocks.reshape(-1)).cuda()
-    scales[:512] = torch.from_numpy(real_scales).cuda()
+    hdiag = (calibration * calibration).mean(0)
+    blocks, scales = ext.encode(weight, hdiag.cuda(), torch.from_numpy(lut).cuda())
+    real_blocks, real_scales = O.encode_linear(weight[:512].cpu(), hdiag, lut)
+    assert np.array_equal(blocks[:real_blocks.size].cpu().numpy(), real_blocks.reshape(-1))
+    assert np.array_equal(scales[:512].cpu().numpy(), real_scales)
     x = torch.randn(tokens, k, device="cuda", generator=gen).bfloat16()
     handle = ext.pack_encoded_device(blocks, scales)
     try:
