@@ -81,7 +81,12 @@ int tx_pack_encoded_shard(const uint8_t *blocks, size_t nbytes, const float *sca
  * to bf16 first; this build does not, which is inside the operator's tolerance).  TX_DTYPE_F16: the fp16 twin
  * (texelator_bc4_kernel, :94-139, un-rounded weight, fp32 accumulation, one fp16 rounding; for tokens >=
  * prefill_threshold the reference goes through fp16(pal*scale) and cuBLAS, :996-1046): the same kernels, the
- * fp16 activations are the tensor-core operand as they are. */
+ * fp16 activations are the tensor-core operand as they are.
+ * Token groups below the threshold read the matrix once for all rows (the reference launches one grid row per
+ * token, :1438-1468); for groups and for short prompts on matrices with few rows K may be cut into ranges whose
+ * fp32 sums a second kernel adds in a fixed order (results repeat bit for bit; they can differ in the last bit
+ * from the same rows taken one at a time).  All calls on one device share one activation scratch and one
+ * partial-sum scratch: order them on one stream. */
 int tx_linear(uint64_t handle, const void *x, void *y, int tokens, int dtype, void *stream);
 
 /* No counterpart in the reference.  The result of tx_linear for a small token group (1..32 tokens,
