@@ -498,7 +498,8 @@ def run_gpu_arm(args, config) -> None:
     device = torch.device("cuda", local)
     prompt, decode = args.prompt, args.decode
     max_len = prompt + decode + args.warmup + 16
-    model = BC4Decoder(config, device, max_len, seed=1234, tp_rank=rank, tp_world=world, lookahead=args.lookahead)
+    model = BC4Decoder(config, device, max_len, seed=1234, tp_rank=rank, tp_world=world, lookahead=args.lookahead,
+                       encoder=args.encoder)
     ids = torch.randint(0, config.vocab, (prompt,), generator=torch.Generator().manual_seed(0))
     model.prefill(ids)
     model.tok.fill_(int(ids[-1]))
@@ -754,6 +755,8 @@ def main() -> None:
                         help="--batch: B >= 16 through the multi-token decode kernel (gemv), the tensor-core tile kernel (tiles), "
                              "or whichever measures faster per projection (tuned)")
     parser.add_argument("--threshold", type=int, default=16, help="--micro: prefill threshold (token counts below it take the decode kernel)")
+    parser.add_argument("--encoder", default="minmax", choices=["minmax", "e3"],
+                        help="how the synthetic weights are BC4-encoded: the encoder's min/max start, or its whole endpoint search on the GPU")
     parser.add_argument("--fuse-norm", action="store_true", help="residual add + RMSNorm inside the qkv and gate/up linears (A/B aid; default: separate norm kernels)")
     parser.add_argument("--micro-exchange", action="store_true", help="tensor parallel: time the exchange alone (1000 in one graph)")
     parser.add_argument("--micro", default=None, help="MxK[xT]: time one linear shape alone (profiling aid)")

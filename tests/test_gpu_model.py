@@ -171,3 +171,28 @@ def test_configuration_2_model_gate():
         model.check_status()
     finally:
         model.free()
+
+
+def test_model_with_weights_from_the_gpu_encoder():
+    """The harness with its projections encoded by the reference's endpoint search on the GPU (`encoder="e3"`):
+    same gates as with the min/max encoding -- the operator against dense dequantised weights, eager and graph."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from texelator_b200.modeling import CONFIGS, BC4Decoder
+    model = BC4Decoder(CONFIGS["toy128"], "cuda:0", max_len=96, seed=21, keep_dense=True, encoder="e3")
+    try:
+        ids = torch.randint(0, model.config.vocab, (40,), generator=torch.Generator().manual_seed(22))
+        assert _cosine(model.prefill(ids), model.prefill(ids, dense=True)) >= 0.999
+        model.prefill(ids)
+        model.tok.fill_(int(ids[-1]))
+        state = (model.tok.clone(), model.pos.clone(), model.mask.clone())
+        model.decode_eager(dense=True)
+        want = model.last_hidden.clone()
+        model.tok.copy_(state[0]); model.pos.copy_(state[1]); model.mask.copy_(state[2])
+        model.capture()
+        model.decode_graph()
+        model.stream.synchronize()
+        assert _cosine(model.last_hidden, want) >= 0.999
+        model.check_status()
+    finally:
+        model.free()

@@ -157,9 +157,12 @@ class BC4Decoder:
 
     def __init__(self, config: DecoderConfig, device, max_len: int, seed: int = 0, tp_rank: int = 0,
                  tp_world: int = 1, group=None, lookahead: int = 3, keep_dense: bool = False,
-                 weight_std: float = 0.02, prefill_backend: int = 5):
+                 weight_std: float = 0.02, prefill_backend: int = 5, encoder: str = "minmax"):
         self.config, self.device, self.max_len = config, torch.device(device), max_len
         self.rank, self.world, self.group = tp_rank, tp_world, group
+        if encoder not in ("minmax", "e3"):
+            raise ValueError("encoder must be 'minmax' (endpoints at the block's extremes) or 'e3' (the reference's endpoint search)")
+        self.encoder = encoder
         self.ext = runtime.extension()
         c = config
         if c.q_heads % tp_world or c.kv_heads % tp_world or (c.intermediate // 16) % tp_world or (c.q_rows // 16) % tp_world:
@@ -273,14 +276,25 @@ class BC4Decoder:
             self.dense.append((handle, self.ext.dequant(handle, runtime.DEQUANT_SCALED_BF16), bias))
         return handle
 
+    def _encode(self, weight, lut):
+        """BC4 blocks and row scales of one projection: ``minmax`` is the start of the reference's encoder
+        (texelator/encoder.py:46-51) written with torch ops; ``e3`` its whole activation-weighted endpoint search
+        (:34-102) on the GPU (``tx_encode``), weighted by the second moments of 64 seeded N(0,1) calibration rows
+        (drawn per K from a generator of their own, so every rank of a tensor-parallel model uses the same)."""
+        if self.encoder == "minmax":
+            return encode_minmax_cuda(weight, lut)
+        k = weight.shape[1]
+        calibration = torch.randn(64, k, device=self.device, generator=torch.Generator(device=self.device).manual_seed(1000003 + k))
+        return self.ext.encode(weight.float().contiguous(), (calibration * calibration).mean(0), lut)
+
     def _pack_rows(self, weight, lut, bias):
-        blocks, scales = encode_minmax_cuda(weight, lut)
+        blocks, scales = self._encode(weight, lut)
         return self._register(self.ext.pack_encoded_device(blocks, scales, bias), bias)
 
     def _pack_columns(self, weight, lut):
         """Row-parallel shard: encode the full matrix (row scales come from full rows), keep this
         rank's 16-column blocks of every row."""
-        blocks, scales = encode_minmax_cuda(weight, lut)
+        blocks, scales = self._encode(weight, lut)
         if self.world > 1:
             m, k = weight.shape
             per = (k // 16) // self.world
